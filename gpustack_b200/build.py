@@ -35,6 +35,9 @@ SOURCES = [
     "latent_attention_mma.cu",
     "gemm_simt_grouped.cu",
     "moe_biased.cu",
+    "prenorm.cu",
+    "rot_prep.cu",
+    "linear_attn.cu",
 ]
 # What a layer-list decoder (attention with a softmax sink / matrix-memory recurrence, norm after the
 # sum) launches: a fresh checkout that only serves such a model compiles these and nothing else.
@@ -62,10 +65,29 @@ STREAMS_LATENT_SOURCES = [
     "attention_sink.cu",
 ]
 ROUTED_SOURCES = ["moe.cu", "moe_biased.cu"]
+# What a pre-norm decoder with one norm per layer (mixer and feed-forward side by side), rotary attention in a
+# sliding window and decayed linear attention launches; routed feed-forwards add ROUTED_SOURCES
+PARALLEL_SOURCES = [
+    "runtime.cu",
+    "elementwise.cu",
+    "gemm_tcgen05.cu",
+    "gemm_simt.cu",
+    "gemm_simt_grouped.cu",
+    "streams.cu",
+    "prenorm.cu",
+    "rot_prep.cu",
+    "attention_sink.cu",
+    "linear_attn.cu",
+]
 
 
 def layer_list_sources(mcfg):
     """(tag, sources) of the library a process serving this layer-list model needs."""
+    if getattr(mcfg, "residual", "post_ln") == "parallel":
+        routed = any(l.mlp is not None and l.mlp.kind == "moe" for l in mcfg.layers)
+        tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)
+        tag = "parallel" + ("_routed" if routed else "") + ("_tc" if tc else "")
+        return tag, PARALLEL_SOURCES + (ROUTED_SOURCES if routed else []) + (ATTENTION_TC_SOURCES if tc else [])
     if getattr(mcfg, "residual", "post_ln") == "streams":
         routed = any(l.mlp is not None and l.mlp.kind == "moe" for l in mcfg.layers)
         return ("streams_routed", STREAMS_LATENT_SOURCES + ROUTED_SOURCES) if routed else ("streams", list(STREAMS_LATENT_SOURCES))

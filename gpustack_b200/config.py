@@ -15,7 +15,7 @@ from typing import Optional
 
 SUPPORTED_ARCHS = ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM")
 # designs whose config.json lists their layers one by one (LayerListConfig below)
-LAYER_LIST_ARCHS = ("Vodavik", "Danipel")
+LAYER_LIST_ARCHS = ("Vodavik", "Danipel", "Resevik")
 
 
 @dataclass
@@ -215,7 +215,8 @@ class AttentionSpec:
     """Softmax attention mixer of a layer-list design.  Every option is a parameter, so another design can
     combine them differently: separate key / value widths, per-head RMS norm of q and k, a query
     temperature 1 + coef * ln(floor((p + 1) / every) + 1), a learned softmax sink, a sigmoid output
-    gate, q/k/v biases, keys and values taken from an earlier layer's cache (kv_from)."""
+    gate, q/k/v biases, keys and values taken from an earlier layer's cache (kv_from), rotary positions,
+    a weightless q/k norm after the rotation, a sliding window, values that are the unrotated keys."""
     heads: int
     kv_heads: int
     dim: int                       # query / key width per head
@@ -228,6 +229,10 @@ class AttentionSpec:
     q_temp_coef: float = 0.0
     q_temp_every: int = 0          # 0 = no temperature
     kv_from: Optional[int] = None  # layer index whose cache this mixer reads
+    rot: Optional["RotarySpec"] = None   # rotary positions on q and k (before the unit norm), None = no rotation
+    qk_unit_norm: bool = False     # q and k over their root mean square per head AFTER the rotation, no weight
+    window: int = 0                # > 0: position i sees j with 0 <= i - j < window
+    values_are_keys: bool = False  # no value projection: v = k as projected (before rotation and norm); vdim == dim
 
     kind = "attention"
 
@@ -239,7 +244,7 @@ class AttentionSpec:
     def tile_sized(self) -> bool:
         """Keys and values share one width that is a tensor-core tile (64 / 128) and the group fits the decode
         kernel: the Llama-class attention kernels (with sink and gate) can serve this mixer in bf16."""
-        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
+        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16 and not self.window
 
     @property
     def out_width(self) -> int:
@@ -259,6 +264,36 @@ class MLSTMSpec:
     @property
     def out_width(self) -> int:
         return self.heads * self.vdim
+
+
+@dataclass
+class LinearAttentionSpec:
+    """Linear attention with a fixed decay per head and no softmax or denominator: per head a state S (dim x vdim,
+    fp32, zero before a sequence's first token), S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t.  Options:
+    a feature map on q, k and v ("silu" or None), rotary positions on q and k, a factor on k (after the rotation),
+    the output norm ("all_heads": one RMS norm with a weight over the concatenated heads; "per_head": every head
+    over its own root mean square, no weight) and the output gate's activation ("sigmoid" | "silu")."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+    feature: Optional[str] = None
+    rot: Optional["RotarySpec"] = None
+    k_scale: float = 1.0
+    out_norm: str = "per_head"
+    gate_act: str = "sigmoid"
+    type_name: str = "linear_attention"
+
+    kind = "linear_attention"
+
+    @property
+    def out_width(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def proj_rows(self) -> int:
+        """Rows of the fused projection [q | k | v | gate]."""
+        return 2 * self.heads * self.dim + 2 * self.out_width
 
 
 @dataclass
@@ -357,6 +392,13 @@ class MoESpec:
     scale: float = 1.0
     shared_ff: int = 0
     shared_limit: float = 0.0
+    # other routed designs: score "sigmoid" = sigmoid(z) per output instead of the softmax; renormalize False = the
+    # chosen scores are the weights as they are; weight_on "input" = an expert runs on weight * x (its output is not
+    # scaled again); act = the experts' gate activation ("clamped_swish" above | "silu": down(silu(gate x) * up x))
+    score: str = "softmax"
+    renormalize: bool = True
+    weight_on: str = "output"
+    act: str = "clamped_swish"
 
 
 @dataclass
@@ -388,8 +430,15 @@ class LayerListConfig:
     # residual scheme: "post_ln" (x <- LN(alpha x + f(x))) or "streams" (pre-norm; `streams` parallel copies of
     # the residual joined by learned scalars: u = sum_s in[s] x_s, y = f(norm(u)),
     # x_t <- sum_s mix[s, t] x_s + residual_mult * out[t] * y; streams == 0: one stream, x <- x + residual_mult * y)
+    # "parallel": pre-norm with ONE norm per layer whose output feeds the mixer and the feed-forward side by side,
+    # x <- x + mixer(norm(x)) + ff(norm(x))
     residual: str = "post_ln"
-    norm: str = "layernorm"                    # "layernorm" (bias-free) | "tanh": tanh(alpha x) w + b, no statistics
+    norm: str = "layernorm"                    # "layernorm" (bias-free) | "tanh": tanh(alpha x) w + b, no statistics | "rms"
+    # layers loop_start .. loop_stop-1 run loop_times times in a row with the same weights (every pass with its own
+    # cache / state); before each pass but the first the embedding output is added to the residual
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
     streams: int = 0
     residual_mult: float = 1.0
     embed_scale: float = 1.0
@@ -409,10 +458,21 @@ class LayerListConfig:
     def num_hidden_layers(self) -> int:
         return len(self.layers)
 
+    def runs(self) -> list:
+        """The order in which the layers run: [(layer index, True when the embedding output is added to the
+        residual right before it)].  Caches and recurrent state belong to a RUN, weights to a layer."""
+        a, b = self.loop_start, self.loop_stop
+        if self.loop_times == 1 or b <= a:
+            return [(l, False) for l in range(len(self.layers))]
+        out = [(l, False) for l in range(a)]
+        for p in range(self.loop_times):
+            out += [(l, p > 0 and l == a) for l in range(a, b)]
+        return out + [(l, False) for l in range(b, len(self.layers))]
+
     @property
     def has_state(self) -> bool:
         """True when some mixer carries a recurrent state per sequence (needs a state slot; no prefix reuse)."""
-        return any(l.mixer.kind == "mlstm" for l in self.layers)
+        return any(l.mixer.kind in ("mlstm", "linear_attention") for l in self.layers)
 
     def kv_owner(self, l: int) -> Optional[int]:
         """Layer whose K/V cache layer l's attention reads (itself unless kv_from), None for other mixers."""
@@ -427,16 +487,18 @@ class LayerListConfig:
         return max(1, self.streams)
 
     def kv_bytes_per_token(self, tp: int = 1, elem_bytes: int = 2) -> int:
-        n = sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in (l.mixer for l in self.layers)
-                if m.kind == "attention" and m.kv_from is None)
-        return n + sum(m.cache_width * elem_bytes for m in (l.mixer for l in self.layers) if m.kind == "latent_attention")
+        mixers = [self.layers[l].mixer for l, _ in self.runs()]
+        n = sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in mixers if m.kind == "attention" and m.kv_from is None)
+        return n + sum(m.cache_width * elem_bytes for m in mixers if m.kind == "latent_attention")
 
     def state_bytes_per_seq(self) -> int:
         n = 0
-        for m in (l.mixer for l in self.layers):
+        for m in (self.layers[l].mixer for l, _ in self.runs()):
             if m.kind == "mlstm":
                 z = (m.vdim + 31) // 32
                 n += 4 * m.heads * (m.dim * m.vdim + z * m.dim + z)
+            elif m.kind == "linear_attention":
+                n += 4 * m.heads * m.dim * m.vdim
         return n
 
     def weight_bytes(self, tp: int = 1, quantization: Optional[str] = None) -> int:
@@ -444,8 +506,10 @@ class LayerListConfig:
         for l in self.layers:
             m = l.mixer
             if m.kind == "attention":
-                kv = 0 if m.kv_from is not None else m.kv_heads * (m.dim + m.vdim)
+                kv = 0 if m.kv_from is not None else m.kv_heads * (m.dim + (0 if m.values_are_keys else m.vdim))
                 n += D * (m.q_width + kv + (m.out_width if m.gate else 0)) + m.out_width * D
+            elif m.kind == "linear_attention":
+                n += D * m.proj_rows + m.out_width * D
             elif m.kind == "latent_attention":
                 n += D * m.proj_rows + (m.q_rank * m.q_width if m.q_rank else 0) \
                     + m.kv_rank * m.heads * (m.dim + m.vdim) + m.out_width * D
@@ -465,6 +529,8 @@ class LayerListConfig:
             raise ValueError(f"unsupported architecture {arch}; layer-list designs: {LAYER_LIST_ARCHS}")
         if arch == "Danipel":
             return _danipel_from_dict(d)
+        if arch == "Resevik":
+            return _resevik_from_dict(d)
         layers = []
         for i, e in enumerate(d["layers"]):
             mx = e["mixer"]
@@ -503,6 +569,8 @@ class LayerListConfig:
         """config.json of this model (the inverse of from_dict)."""
         if self.architecture == "Danipel":
             return _danipel_to_dict(self)
+        if self.architecture == "Resevik":
+            return _resevik_to_dict(self)
         out = []
         for l in self.layers:
             m = l.mixer
@@ -592,6 +660,93 @@ def _danipel_to_dict(c: "LayerListConfig") -> dict:
     if c.streams:
         d["streams"] = c.streams
     return d
+
+
+def _resevik_from_dict(d: dict) -> "LayerListConfig":
+    """Resevik: pre-norm layers whose ONE RMS norm feeds mixer and feed-forward side by side; mixers "lightning"
+    (decayed linear attention, SiLU feature map, all heads normed together with a weight, sigmoid gate), "retention"
+    (decayed linear attention, half-split rotation, k / sqrt(dim), every head over its own root mean square, SiLU gate)
+    and "attention" (grouped softmax attention in a sliding window; interleaved rotation, then a weightless RMS
+    norm of q and k; the values are the unrotated keys); a routed feed-forward whose sigmoid scores multiply the
+    chosen experts' input; a span of layers run `times` times in a row."""
+    layers = []
+    for i, e in enumerate(d["layers"]):
+        mx, kind = e["mixer"], e["type"]
+
+        def rotary(layout):
+            r = mx["rot"]
+            rot = RotarySpec(dims=int(r["dims"]), base=float(r["base"]), layout=layout)
+            if rot.dims % 2 or rot.dims <= 0 or rot.dims > int(mx["dim"]):
+                raise ValueError(f"layer {i}: rot.dims {rot.dims} must be even and at most dim {mx['dim']}")
+            return rot
+
+        if kind == "attention":
+            spec = AttentionSpec(heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                                 vdim=int(mx.get("vdim", mx["dim"])), scale=float(mx["scale"]), qk_norm=False,
+                                 qkv_bias=False, sink=False, gate=False, rot=rotary("interleaved"), qk_unit_norm=True,
+                                 window=int(mx["mask"]["size"]), values_are_keys=True)
+            if spec.heads % spec.kv_heads:
+                raise ValueError(f"layer {i}: heads {spec.heads} not a multiple of kv_heads {spec.kv_heads}")
+            if spec.vdim != spec.dim:
+                raise ValueError(f"layer {i}: the values are the keys, so vdim {spec.vdim} must equal dim {spec.dim}")
+            if spec.window < 1:
+                raise ValueError(f"layer {i}: mask.size {spec.window} must be at least 1")
+        elif kind in ("lightning", "retention"):
+            decay = tuple(float(x) for x in mx["decay"])
+            if len(decay) != int(mx["heads"]):
+                raise ValueError(f"layer {i}: {len(decay)} decays for {mx['heads']} heads")
+            ret = kind == "retention"
+            spec = LinearAttentionSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                                       decay=decay, feature=None if ret else "silu", rot=rotary("half") if ret else None,
+                                       k_scale=int(mx["dim"]) ** -0.5 if ret else 1.0,
+                                       out_norm="per_head" if ret else "all_heads", gate_act="silu" if ret else "sigmoid",
+                                       type_name=kind)
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        mlp = e.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind") != "moe":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+            ro, ex = mlp["router"], mlp["expert"]
+            moe = MoESpec(experts=int(ro["experts"]), top=int(ro["top"]), ff=int(ex["ff"]), limit=0.0, score="sigmoid",
+                          renormalize=False, weight_on="input", act="silu")
+            if not 1 <= moe.top <= moe.experts:
+                raise ValueError(f"layer {i}: top {moe.top} of {moe.experts} experts")
+            mlp = MLPSpec(kind="moe", ff=moe.ff, act="silu", moe=moe)
+        layers.append(LayerSpec(mixer=spec, mlp=mlp))
+    lp = d.get("loop") or {}
+    a, b, times = int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1))
+    if times < 1 or not (0 <= a <= b <= len(layers)):
+        raise ValueError(f"loop {lp}: needs 0 <= start <= stop <= {len(layers)} and times >= 1")
+    eos_all = _eos_of(d)
+    return LayerListConfig(architecture="Resevik", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                           norm_eps=float(d["norm"]["eps"]), residual="parallel", norm="rms",
+                           embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), loop_start=a, loop_stop=b,
+                           loop_times=times, eos_token_ids=eos_all, eos_token_id=eos_all[0] if eos_all else None,
+                           bos_token_id=d.get("bos_token_id"))
+
+
+def _resevik_to_dict(c: "LayerListConfig") -> dict:
+    out = []
+    for l in c.layers:
+        m = l.mixer
+        if m.kind == "attention":
+            mx = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+                  "mask": {"size": m.window}, "rot": m.rot.to_dict()}
+            kind = "attention"
+        else:
+            mx = {"heads": m.heads, "dim": m.dim, "vdim": m.vdim, "decay": list(m.decay)}
+            if m.rot is not None:
+                mx["rot"] = m.rot.to_dict()
+            kind = m.type_name
+        mlp = None
+        if l.mlp is not None:
+            e = l.mlp.moe
+            mlp = {"kind": "moe", "expert": {"ff": e.ff}, "router": {"experts": e.experts, "top": e.top}}
+        out.append({"type": kind, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Resevik", "vocab": c.vocab_size, "width": c.hidden_size, "layers": out,
+            "norm": {"eps": c.norm_eps}, "embedding": {"scale": c.embed_scale},
+            "loop": {"start": c.loop_start, "stop": c.loop_stop, "times": c.loop_times}}
 
 
 # Named shapes used by tests and bench (random-init; there are no checkpoints offline).

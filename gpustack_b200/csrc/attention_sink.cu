@@ -5,7 +5,9 @@
 //   * a learned per-head SINK: exp(sink_h) is added to the softmax denominator (a virtual key whose
 //     score is sink_h, unscaled, and whose value is zero),
 //   * a sigmoid output gate read from the same fused projection as the queries,
-//   * keys / values that belong to an earlier layer's cache (the caller passes that cache).
+//   * keys / values that belong to an earlier layer's cache (the caller passes that cache),
+//   * a sliding window (position i sees j with 0 <= i - j < window; 0 = every earlier key): key blocks that lie
+//     wholly before the window are never read.
 // Three kernels: `attn_prep` (bias + norms + temperature, in place for q, scatter of k and v into
 // the pages), `prefill` (a tile of 16 query rows of one sequence per CTA, keys staged in shared
 // memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps take
@@ -190,7 +192,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
                          const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
                          const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                          const float* __restrict__ sink, TA* out, int64_t ldo, int H, int G, int dk, int dv, int page,
-                         float scale, int64_t v_ld) {
+                         float scale, int64_t v_ld, int window) {
   extern __shared__ float smem[];
   float* Qs = smem;                                   // [16][dk]
   float* Ks = Qs + kPfRows * dk;                      // [32][dk + 1]
@@ -217,8 +219,10 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
 #pragma unroll
     for (int j = 0; j < kMaxDvPerLane; ++j) acc[r][j] = 0.f;
   }
-  const int kv_end = ctx + q0 + nrows;                // keys this tile can see: [0, kv_end)
-  for (int k0 = 0; k0 < kv_end; k0 += kPfKeys) {
+  const int kv_end = ctx + q0 + nrows;                // keys this tile can see: [kv_begin, kv_end)
+  // a sliding window: position i sees j with 0 <= i - j < window, so nothing before the first row's window is read
+  const int kv_begin = window > 0 ? max(0, ctx + q0 - window + 1) : 0;
+  for (int k0 = kv_begin & ~(kPfKeys - 1); k0 < kv_end; k0 += kPfKeys) {
     __syncthreads();                                  // previous block's K / V fully consumed (and Qs written)
     // each warp stages 8 keys
     for (int jj = 0; jj < kPfKeys / kPfWarps; ++jj) {
@@ -251,7 +255,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
 #pragma unroll
     for (int r = 0; r < kPfRowsPerWarp; ++r) {
       const int qpos = ctx + q0 + warp * kPfRowsPerWarp + r;
-      const bool seen = (k0 + lane) <= qpos && (k0 + lane) < kv_end;
+      const bool seen = (k0 + lane) <= qpos && (k0 + lane) < kv_end && (window <= 0 || qpos - (k0 + lane) < window);
       const float sv = seen ? sc[r] * scale : -CUDART_INF_F;
       const float mn = fmaxf(m[r], warp_max(sv));
       float p = 0.f, corr = 1.f;
@@ -315,7 +319,7 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
-                        int H, int G, int dk, int dv, int page, float scale, int64_t v_ld) {
+                        int H, int G, int dk, int dv, int page, float scale, int64_t v_ld, int window) {
   __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
   extern __shared__ __align__(16) float sm_dyn[];      // [dk (padded to 8)] query, then [warps][dv] partial outputs
   constexpr int E = 16 / (int)sizeof(TA);               // elements per 16-byte load
@@ -333,9 +337,12 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
   if (warp == 0 && sink != nullptr) { m = sink[h]; l = 1.f; }
 #pragma unroll
   for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] = 0.f;
-  for (int k0 = warp * 32; k0 < n; k0 += kDecWarps * 32) {
+  // a sliding window: the row at position n - 1 sees keys [n - window, n); the first block read is the one that holds
+  // the window's first key
+  const int first = window > 0 ? max(0, n - window) : 0;
+  for (int k0 = (first & ~31) + warp * 32; k0 < n; k0 += kDecWarps * 32) {
     const int key = k0 + lane;
-    const bool live = key < n;
+    const bool live = key < n && key >= first;
     size_t base = 0;
     float sc = -CUDART_INF_F;
     if (live) {
@@ -354,14 +361,14 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
       }
       sc = a;
     }
-    const float mn = fmaxf(m, warp_max(sc));            // finite: key k0 of this block is live
+    const float mn = fmaxf(m, warp_max(sc));            // finite: some key of this block is live
     const float corr = expf(m - mn), p = live ? expf(sc - mn) : 0.f;
     l = l * corr + warp_sum(p);
     m = mn;
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
     const int cnt = min(32, n - k0);
-    for (int j = 0; j < cnt; ++j) {
+    for (int j = max(0, first - k0); j < cnt; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
       const TA* vp = v_cache + (size_t)bj * v_ld;
@@ -453,12 +460,12 @@ extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias,
 
 extern "C" int b200_attn_sink_prefill_tile(void) { return kPfRows; }
 
-extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                      const void* v_cache, const int32_t* block_table, int max_blocks,
-                                      const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
-                                      const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
-                                      int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
-                                      void* stream) {
+extern "C" int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                         const void* v_cache, const int32_t* block_table, int max_blocks,
+                                         const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                         const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                         int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                         int window, void* stream) {
   if (v_ld <= 0) v_ld = dv;
   B200_REQUIRE(v_ld >= dv, "attn_sink_prefill: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(tile_rows > 0 && tile_rows % kPfRows == 0, "attn_sink_prefill: tiles of %d rows (multiples of %d)",
@@ -477,7 +484,7 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
       cudaFuncSetAttribute(attn_sink_prefill_kernel<TA, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     attn_sink_prefill_kernel<TA, L><<<grid, kPfWarps * 32, smem, s>>>(                                             \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, cu_q,       \
-        ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld);                        \
+        ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window);                \
   } while (0)
   const bool wide = dv > 256;
   if (f32) { if (wide) B200_PF(float, 16); else B200_PF(float, 8); }
@@ -486,10 +493,22 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
   return b200_check_launch("b200_attn_sink_prefill");
 }
 
-extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                     const void* v_cache, const int32_t* block_table, int max_blocks,
-                                     const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
-                                     int G, int dk, int dv, int page, float scale, int64_t v_ld, void* stream) {
+extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                      const void* v_cache, const int32_t* block_table, int max_blocks,
+                                      const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                      const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                      int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                      void* stream) {
+  return b200_attn_sink_prefill_ex(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, cu_q, ctx_lens,
+                                   tile_seq, tile_q0, n_tiles, tile_rows, sink, out, ldo, H, G, dk, dv, page, scale, v_ld, 0,
+                                   stream);
+}
+
+extern "C" int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                        const void* v_cache, const int32_t* block_table, int max_blocks,
+                                        const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                        int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
+                                        void* stream) {
   if (v_ld <= 0) v_ld = dv;
   B200_REQUIRE(v_ld >= dv, "attn_sink_decode: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvLanes && page > 0,
@@ -505,13 +524,21 @@ extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int 
   if (dv > 256)                                                                                                  \
     attn_sink_decode_kernel<TA, V, 16><<<grid, kDecWarps * 32, smem, s>>>(                                       \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens, \
-        sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld);                                                   \
+        sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window);                                           \
   else                                                                                                           \
     attn_sink_decode_kernel<TA, V, 8><<<grid, kDecWarps * 32, smem, s>>>(                                        \
       (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
-      sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld)
+      sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window)
   if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }
   else { if (vec) B200_DEC(bf16, true); else B200_DEC(bf16, false); }
 #undef B200_DEC
   return b200_check_launch("b200_attn_sink_decode");
+}
+
+extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_table, int max_blocks,
+                                     const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                     int G, int dk, int dv, int page, float scale, int64_t v_ld, void* stream) {
+  return b200_attn_sink_decode_ex(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, seq_lens, B, sink, out,
+                                  ldo, H, G, dk, dv, page, scale, v_ld, 0, stream);
 }

@@ -6,7 +6,8 @@
 //               (tile_expert[], num_tiles[] from moe_align with block_x = 64); a tile multiplies by its expert's
 //               matrix, tiles of experts >= n_real (identity experts) and unused tiles are skipped; the input
 //               rows may be gathered through row_pair (row -> pair -> token = pair / top_k, -1 = padding) and
-//               the output rows multiplied by row_scale (the routing weight);
+//               the output rows multiplied by row_scale (the routing weight) -- or, scale_in, the INPUT rows: the
+//               accumulators are multiplied before the activation, which is the product of the scaled row;
 //   * gated:    W holds interleaved rows (2n = gate_n, 2n + 1 = up_n), both products are accumulated and the
 //               output is  act(g) * u'  computed in fp32 from the fp32 accumulators, rounded once:
 //                 act 1  gelu_tanh(g) * u        gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
@@ -56,6 +57,7 @@ struct GsArgs {
   const float* row_scale;            // NULL: none
   int act;                           // 0 = plain linear
   float limit;
+  int scale_in;                      // 1: row_scale multiplies the row's INPUT (the accumulators before the activation)
 };
 
 template <typename TX, typename TY, bool GATED>
@@ -150,8 +152,14 @@ gemm_simt_grouped_kernel(GsArgs a) {
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc[i][j];
-      if (GATED) v = gated_act(v, accu[i][j], a.act, a.limit);
-      gs_out(Y + (int64_t)m * a.ldy + n, v * rs);
+      if (a.scale_in) {              // W (rs x) = rs (W x): the product is linear in the row
+        v *= rs;
+        if (GATED) v = gated_act(v, accu[i][j] * rs, a.act, a.limit);
+      } else {
+        if (GATED) v = gated_act(v, accu[i][j], a.act, a.limit);
+        v *= rs;
+      }
+      gs_out(Y + (int64_t)m * a.ldy + n, v);
     }
   }
 }
@@ -168,11 +176,11 @@ static int launch_gs(const GsArgs& a, int batch, cudaStream_t s) {
 
 using namespace b200;
 
-extern "C" int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,
-                                        int64_t ldx, int64_t ldw, int64_t ldy, int batch, int64_t bsx, int64_t bsw,
-                                        int64_t bsy, const int32_t* row_pair, int top_k, const int32_t* tile_expert,
-                                        const int32_t* num_tiles, int n_real, int64_t w_expert, const float* row_scale,
-                                        int act, float limit, void* stream) {
+extern "C" int b200_linear_simt_grouped_ex(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,
+                                           int64_t ldx, int64_t ldw, int64_t ldy, int batch, int64_t bsx, int64_t bsw,
+                                           int64_t bsy, const int32_t* row_pair, int top_k, const int32_t* tile_expert,
+                                           const int32_t* num_tiles, int n_real, int64_t w_expert, const float* row_scale,
+                                           int act, float limit, int scale_in, void* stream) {
   B200_REQUIRE(M >= 0 && N > 0 && K > 0 && batch >= 1, "linear_simt_grouped: bad shape M=%d N=%d K=%d batch=%d", M, N, K, batch);
   B200_REQUIRE(ldx >= K && ldw >= K && ldy >= N, "linear_simt_grouped: leading dimensions too small");
   B200_REQUIRE(act >= 0 && act <= 3, "linear_simt_grouped: unknown activation %d", act);
@@ -180,12 +188,21 @@ extern "C" int b200_linear_simt_grouped(const void* X, int x_f32, const void* W,
   B200_REQUIRE(row_pair == nullptr || top_k >= 1, "linear_simt_grouped: top_k");
   if (M == 0) return B200_OK;
   GsArgs a{X, (const bf16*)W, Y, M, N, K, ldx, ldw, ldy, bsx, bsw, bsy, row_pair, top_k, tile_expert, num_tiles, n_real,
-           w_expert, row_scale, act, limit};
+           w_expert, row_scale, act, limit, (scale_in && row_scale != nullptr) ? 1 : 0};
   cudaStream_t s = (cudaStream_t)stream;
   if (x_f32 && y_f32) return launch_gs<float, float>(a, batch, s);
   if (x_f32) return launch_gs<float, bf16>(a, batch, s);
   if (y_f32) return launch_gs<bf16, float>(a, batch, s);
   return launch_gs<bf16, bf16>(a, batch, s);
+}
+
+extern "C" int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,
+                                        int64_t ldx, int64_t ldw, int64_t ldy, int batch, int64_t bsx, int64_t bsw,
+                                        int64_t bsy, const int32_t* row_pair, int top_k, const int32_t* tile_expert,
+                                        const int32_t* num_tiles, int n_real, int64_t w_expert, const float* row_scale,
+                                        int act, float limit, void* stream) {
+  return b200_linear_simt_grouped_ex(X, x_f32, W, Y, y_f32, M, N, K, ldx, ldw, ldy, batch, bsx, bsw, bsy, row_pair, top_k,
+                                     tile_expert, num_tiles, n_real, w_expert, row_scale, act, limit, 0, stream);
 }
 
 extern "C" int b200_simt_group_rows(void) { return kGsBM; }

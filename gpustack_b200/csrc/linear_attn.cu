@@ -1,0 +1,323 @@
+// Linear attention with a fixed decay per head: no softmax, no denominator, state in fp32.
+//
+// Per head, with the constant decay d_h:
+//     S_t = d_h S_{t-1} + k_t v_t^T          (S: dk x dv, zero before a sequence's first token)
+//     o_t = S_t^T q_t
+// Queries, keys and values arrive as fp32 rows (the per-head preparation -- feature map, rotation, factors -- has
+// been applied; rot_prep.cu); the state of slot s is S [slots][H][dv][dk] (key index fastest), so that a warp's
+// loads and stores are contiguous.  A sequence whose context is empty starts from zero, whatever the slot held
+// before: a slot that is handed to a new sequence needs no clearing.
+//
+// `linattn_scan`   runs a sequence's new rows in order (the single row of a decode step, or a short portion); grid
+//                  (sequences, heads, ceil(dv / 32)): a CTA owns 32 value columns of one head's state, each of its 8
+//                  warps 4 of them; lane r holds the key rows r, r + 32, ... of those columns in registers; S^T q is
+//                  a warp-shuffle reduction, no block barrier per token.
+// `linattn_chunk`  the same recurrence for prompt portions, 16 rows at a time without a serial dependency inside a
+//                  chunk.  With the state S_0 at the chunk's start and rows t = 0 .. n-1:
+//                      o_t = d^{t+1} S_0^T q_t + sum_{s<=t} d^{t-s} (k_s . q_t) v_s
+//                      S_n = d^n S_0 + sum_s d^{n-1-s} k_s v_s^T
+//                  Every power has a non-negative exponent (nothing is divided by a decay, so a small decay cannot
+//                  overflow); all products and sums are fp32 FMAs, only the grouping of the sums differs from the
+//                  serial form.  The CTA's 32 columns of S live in shared memory for the whole portion.
+// `linattn_out`    closes the mixer: the heads' outputs over their root mean square -- per head without a weight, or
+//                  all heads together with a weight vector -- times sigmoid(g) or silu(g) of the gate columns of the
+//                  fused projection, rounded once to the activation type.
+#include "common.cuh"
+#include "runtime.h"
+#include "../../include/b200.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float la_f32(float v) { return v; }
+__device__ __forceinline__ float la_f32(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void la_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void la_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int kLaWarps = 8, kLaColsPerWarp = 4, kLaCols = kLaWarps * kLaColsPerWarp, kLaTok = 16;
+
+// EPT = key rows per lane = ceil(dk / 32)
+template <int EPT>
+__global__ void __launch_bounds__(kLaWarps * 32)
+linattn_scan_kernel(const float* __restrict__ x, int64_t ld, int q_col, int k_col, int v_col,
+                    const float* __restrict__ decay, const int32_t* __restrict__ cu_seq,
+                    const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, float* S_state,
+                    float* __restrict__ o_raw, int H, int dk, int dv) {
+  extern __shared__ float smem[];
+  float* qs = smem;                                   // [16][dk]
+  float* ks = qs + kLaTok * dk;                       // [16][dk]
+  float* vs = ks + kLaTok * dk;                       // [16][32]
+  const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+  const int slot = state_slots[s];
+  if (slot < 0) return;
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (t1 <= t0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = z * kLaCols + warp * kLaColsPerWarp;
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
+  const float d = decay[h];
+  const bool fresh = ctx_lens[s] == 0;
+  float S[EPT][kLaColsPerWarp];
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int row = lane + 32 * j;
+#pragma unroll
+    for (int c = 0; c < kLaColsPerWarp; ++c)
+      S[j][c] = (!fresh && row < dk && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + row] : 0.f;
+  }
+  if (t1 - t0 == 1) {
+    // a decode row: no staging, no barrier; the state and the inputs are in flight together
+    const float* row = x + (size_t)t0 * ld;
+    float kk[EPT], qq[EPT], v[kLaColsPerWarp], num[kLaColsPerWarp];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const int r = lane + 32 * j;
+      kk[j] = r < dk ? row[k_col + h * dk + r] : 0.f;
+      qq[j] = r < dk ? row[q_col + h * dk + r] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < kLaColsPerWarp; ++c) {
+      v[c] = c0 + c < dv ? row[v_col + h * dv + c0 + c] : 0.f;
+      num[c] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < EPT; ++j)
+#pragma unroll
+      for (int c = 0; c < kLaColsPerWarp; ++c) {
+        S[j][c] = fmaf(d, S[j][c], kk[j] * v[c]);
+        num[c] = fmaf(S[j][c], qq[j], num[c]);
+      }
+#pragma unroll
+    for (int c = 0; c < kLaColsPerWarp; ++c) num[c] = warp_sum(num[c]);
+    if (lane < kLaColsPerWarp && c0 + lane < dv) {
+      float mine = num[0];
+#pragma unroll
+      for (int c = 1; c < kLaColsPerWarp; ++c) mine = lane == c ? num[c] : mine;
+      o_raw[(size_t)t0 * H * dv + h * dv + c0 + lane] = mine;
+    }
+  } else {
+    for (int ch = t0; ch < t1; ch += kLaTok) {
+      const int nt = min(kLaTok, t1 - ch);
+      __syncthreads();                                // every warp is done with the previous chunk
+      for (int i = threadIdx.x; i < nt * dk; i += blockDim.x) {
+        const int tt = i / dk, dd = i - tt * dk;
+        const float* row = x + (size_t)(ch + tt) * ld;
+        qs[i] = row[q_col + h * dk + dd];
+        ks[i] = row[k_col + h * dk + dd];
+      }
+      for (int i = threadIdx.x; i < nt * kLaCols; i += blockDim.x) {
+        const int tt = i / kLaCols, c = z * kLaCols + (i % kLaCols);
+        vs[i] = c < dv ? x[(size_t)(ch + tt) * ld + v_col + h * dv + c] : 0.f;
+      }
+      __syncthreads();
+      for (int tt = 0; tt < nt; ++tt) {
+        float v[kLaColsPerWarp], num[kLaColsPerWarp];
+#pragma unroll
+        for (int c = 0; c < kLaColsPerWarp; ++c) {
+          v[c] = vs[tt * kLaCols + warp * kLaColsPerWarp + c];
+          num[c] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+          const int row = lane + 32 * j;
+          if (row < dk) {
+            const float kk = ks[tt * dk + row], qq = qs[tt * dk + row];
+#pragma unroll
+            for (int c = 0; c < kLaColsPerWarp; ++c) {
+              S[j][c] = fmaf(d, S[j][c], kk * v[c]);
+              num[c] = fmaf(S[j][c], qq, num[c]);
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < kLaColsPerWarp; ++c) num[c] = warp_sum(num[c]);
+        if (lane < kLaColsPerWarp && c0 + lane < dv) {
+          float mine = num[0];
+#pragma unroll
+          for (int c = 1; c < kLaColsPerWarp; ++c) mine = lane == c ? num[c] : mine;
+          o_raw[(size_t)(ch + tt) * H * dv + h * dv + c0 + lane] = mine;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int row = lane + 32 * j;
+    if (row < dk) {
+#pragma unroll
+      for (int c = 0; c < kLaColsPerWarp; ++c)
+        if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + row] = S[j][c];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------- chunk form
+constexpr int kLcTok = 16, kLcThreads = 512;
+
+__global__ void __launch_bounds__(kLcThreads)
+linattn_chunk_kernel(const float* __restrict__ x, int64_t ld, int q_col, int k_col, int v_col,
+                     const float* __restrict__ decay, const int32_t* __restrict__ cu_seq,
+                     const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, float* S_state,
+                     float* __restrict__ o_raw, int H, int dk, int dv) {
+  extern __shared__ float smem[];
+  const int dkp = dk + 1;
+  float* Ssm = smem;                                  // [dk][33]
+  float* qs = Ssm + dk * 33;                          // [16][dk + 1]
+  float* ks = qs + kLcTok * dkp;                      // [16][dk + 1]
+  float* vs = ks + kLcTok * dkp;                      // [16][32]
+  float* A = vs + kLcTok * 32;                        // [16][17]   k_s . q_t
+  float* dp = A + kLcTok * 17;                        // [17]       d^0 .. d^16
+  const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+  const int slot = state_slots[s];
+  if (slot < 0) return;
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (t1 <= t0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c0 = z * 32;
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
+  const bool fresh = ctx_lens[s] == 0;
+  for (int i = tid; i < dk * 32; i += kLcThreads) {
+    const int c = i / dk, r = i - c * dk;             // r fastest: contiguous global reads
+    Ssm[r * 33 + c] = (!fresh && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + r] : 0.f;
+  }
+  if (tid <= kLcTok) dp[tid] = (float)pow((double)decay[h], (double)tid);
+  for (int ch = t0; ch < t1; ch += kLcTok) {
+    const int nt = min(kLcTok, t1 - ch);
+    __syncthreads();                                  // state update of the previous chunk done, inputs free
+    for (int i = tid; i < nt * dk; i += kLcThreads) {
+      const int tt = i / dk, dd = i - tt * dk;
+      const float* row = x + (size_t)(ch + tt) * ld;
+      qs[tt * dkp + dd] = row[q_col + h * dk + dd];
+      ks[tt * dkp + dd] = row[k_col + h * dk + dd];
+    }
+    {
+      const int tt = tid >> 5, c = c0 + (tid & 31);
+      vs[tid] = (tt < nt && c < dv) ? x[(size_t)(ch + tt) * ld + v_col + h * dv + c] : 0.f;
+    }
+    __syncthreads();
+    // (a) k_s . q_t for s <= t
+    if (tid < 256) {
+      const int t = tid >> 4, sx = tid & 15;
+      if (t < nt && sx <= t) {
+        float acc = 0.f;
+        const float* kr = ks + sx * dkp;
+        const float* qr = qs + t * dkp;
+        for (int r = 0; r < dk; ++r) acc = fmaf(kr[r], qr[r], acc);
+        A[t * 17 + sx] = acc;
+      }
+    }
+    __syncthreads();
+    // (b) outputs: thread = (row = warp, column = lane)
+    if (warp < nt) {
+      const int t = warp;
+      float acc = 0.f;
+      const float* qr = qs + t * dkp;
+      for (int r = 0; r < dk; ++r) acc = fmaf(Ssm[r * 33 + lane], qr[r], acc);
+      float num = dp[t + 1] * acc;
+      for (int sx = 0; sx <= t; ++sx) num = fmaf(dp[t - sx] * A[t * 17 + sx], vs[sx * 32 + lane], num);
+      if (c0 + lane < dv) o_raw[(size_t)(ch + t) * H * dv + h * dv + c0 + lane] = num;
+    }
+    __syncthreads();
+    // (c) state update: S[r][c] = d^n S[r][c] + sum_s d^{n-1-s} k_s[r] v_s[c]
+    for (int i = tid; i < dk * 32; i += kLcThreads) {
+      const int r = i >> 5, c = i & 31;
+      float acc = dp[nt] * Ssm[r * 33 + c];
+      for (int sx = 0; sx < nt; ++sx) acc = fmaf(dp[nt - 1 - sx] * ks[sx * dkp + r], vs[sx * 32 + c], acc);
+      Ssm[r * 33 + c] = acc;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * 32; i += kLcThreads) {
+    const int c = i / dk, r = i - c * dk;
+    if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + r] = Ssm[r * 33 + c];
+  }
+}
+
+// ------------------------------------------------------------------------------------------- out
+// One CTA per row.  all_heads: the H * dv outputs are normed together and multiplied by w; otherwise every head is
+// divided by its own root mean square (w optional, dv entries shared by the heads).  gate_act 0 sigmoid, 1 silu.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+linattn_out_kernel(const float* __restrict__ o_raw, const TA* __restrict__ proj, int64_t ld, int gate_col,
+                   const bf16* __restrict__ w, TA* out, int64_t ldo, int H, int dv, int all_heads, int gate_act,
+                   float eps) {
+  extern __shared__ float head_ss[];                  // [H]
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float* o = o_raw + (size_t)t * H * dv;
+  for (int h = warp; h < H; h += nw) {
+    float ss = 0.f;
+    for (int d = lane; d < dv; d += 32) {
+      const float v = o[h * dv + d];
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) head_ss[h] = ss;
+  }
+  __syncthreads();
+  float all = 0.f;
+  if (all_heads) {
+    for (int h = 0; h < H; ++h) all += head_ss[h];     // the same order in every thread
+    all = 1.0f / sqrtf(all / (float)(H * dv) + eps);
+  }
+  const TA* g = proj + (size_t)t * ld + gate_col;
+  for (int i = threadIdx.x; i < H * dv; i += blockDim.x) {
+    const int h = i / dv;
+    const float mul = all_heads ? all : 1.0f / sqrtf(head_ss[h] / (float)dv + eps);
+    float v = o[i] * mul;
+    if (w != nullptr) v *= __bfloat162float(w[all_heads ? i : i - h * dv]);
+    const float gv = la_f32(g[i]);
+    const float sg = 1.0f / (1.0f + expf(-gv));
+    v *= gate_act == 1 ? gv * sg : sg;
+    la_store(out + (size_t)t * ldo + i, v);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_linattn_scan(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* decay,
+                                 const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S,
+                                 float* o_raw, int n_seqs, int H, int dk, int dv, int max_len, void* stream) {
+  B200_REQUIRE(n_seqs >= 0 && H > 0 && dk > 0 && dv > 0 && dk <= 256, "linattn_scan: bad shape H=%d dk=%d dv=%d (dk <= 256)",
+               H, dk, dv);
+  if (n_seqs == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int Z = (dv + kLaCols - 1) / kLaCols;
+  dim3 grid(n_seqs, H, Z);
+  if (max_len > 2) {
+    // prompt portions: the chunk form (a single decode row riding in the same launch is a chunk of one)
+    const size_t smem = sizeof(float) * ((size_t)dk * 33 + 2 * (size_t)kLcTok * (dk + 1) + kLcTok * 32 + kLcTok * 17 + 32);
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(linattn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    linattn_chunk_kernel<<<grid, kLcThreads, smem, s>>>(x, ld, q_col, k_col, v_col, decay, cu_seq, ctx_lens, state_slots, S,
+                                                        o_raw, H, dk, dv);
+    return b200_check_launch("b200_linattn_scan(chunk)");
+  }
+  const size_t smem = sizeof(float) * (2 * (size_t)kLaTok * dk + kLaTok * kLaCols);
+#define B200_LA(E)                                                                                              \
+  linattn_scan_kernel<E><<<grid, kLaWarps * 32, smem, s>>>(x, ld, q_col, k_col, v_col, decay, cu_seq, ctx_lens, \
+                                                           state_slots, S, o_raw, H, dk, dv)
+  if (dk <= 32) B200_LA(1);
+  else if (dk <= 64) B200_LA(2);
+  else if (dk <= 128) B200_LA(4);
+  else B200_LA(8);
+#undef B200_LA
+  return b200_check_launch("b200_linattn_scan");
+}
+
+extern "C" int b200_linattn_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col, const void* w,
+                                void* out, int64_t ldo, int T, int H, int dv, int all_heads, int gate_act, float eps,
+                                void* stream) {
+  B200_REQUIRE(T >= 0 && H > 0 && dv > 0 && H <= 8192, "linattn_out: bad shape");
+  B200_REQUIRE(!all_heads || w != nullptr, "linattn_out: the joint norm has a weight");
+  if (T == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = sizeof(float) * H;
+  if (f32)
+    linattn_out_kernel<float><<<T, 256, smem, s>>>(o_raw, (const float*)proj, ld, gate_col, (const bf16*)w, (float*)out, ldo,
+                                                   H, dv, all_heads, gate_act, eps);
+  else
+    linattn_out_kernel<bf16><<<T, 256, smem, s>>>(o_raw, (const bf16*)proj, ld, gate_col, (const bf16*)w, (bf16*)out, ldo, H,
+                                                  dv, all_heads, gate_act, eps);
+  return b200_check_launch("b200_linattn_out");
+}

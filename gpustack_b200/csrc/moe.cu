@@ -115,7 +115,8 @@ moe_align_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__
 // xp[row, :] = x[row_pair[row] / K, :]  (zero for padding rows), rows < num_tiles[1]
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ row_pair,
-                  const int32_t* __restrict__ num_tiles, bf16* __restrict__ xp, int H, int K, int capacity_rows) {
+                  const int32_t* __restrict__ num_tiles, bf16* __restrict__ xp, int H, int K, int capacity_rows,
+                  const float* __restrict__ row_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int rows = min(num_tiles[1], capacity_rows);
@@ -127,7 +128,16 @@ moe_gather_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ row_pa
     const int vi = (int)(idx % vec_per_row);
     const int pair = row_pair[r];
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (pair >= 0) v = ld_v4(x + (size_t)(pair / K) * H + (size_t)vi * 8);
+    if (pair >= 0) {
+      v = ld_v4(x + (size_t)(pair / K) * H + (size_t)vi * 8);
+      if (row_scale != nullptr) {    // an expert that runs on weight * x: the row is scaled in fp32 and rounded once
+        const float w = row_scale[r];
+        v.x = pack_bf16(bf16_lo(v.x) * w, bf16_hi(v.x) * w);
+        v.y = pack_bf16(bf16_lo(v.y) * w, bf16_hi(v.y) * w);
+        v.z = pack_bf16(bf16_lo(v.z) * w, bf16_hi(v.z) * w);
+        v.w = pack_bf16(bf16_lo(v.w) * w, bf16_hi(v.w) * w);
+      }
+    }
     st_v4(xp + r * (size_t)H + (size_t)vi * 8, v);
   }
 }
@@ -204,14 +214,19 @@ extern "C" int b200_moe_align(const int32_t* topk_ids, const float* topk_w, int 
   return b200_check_launch("b200_moe_align");
 }
 
-extern "C" int b200_moe_gather(const void* x, const int32_t* row_pair, const int32_t* num_tiles, void* xp, int H,
-                               int K, int capacity_rows, void* stream) {
+extern "C" int b200_moe_gather_scaled(const void* x, const int32_t* row_pair, const int32_t* num_tiles, void* xp, int H,
+                                      int K, int capacity_rows, const float* row_scale, void* stream) {
   B200_REQUIRE(H > 0 && H % 8 == 0 && K >= 1, "moe_gather: H=%d must be a multiple of 8", H);
   if (capacity_rows == 0) return B200_OK;
   const size_t items = (size_t)capacity_rows * (H / 8);
   (void)launch_pdl_cls(kPdlMoe, moe_gather_kernel, dim3(moe_grid(items, 256)), dim3(256), 0, (cudaStream_t)stream, 1,
-                   (const bf16*)x, row_pair, num_tiles, (bf16*)xp, H, K, capacity_rows);
+                   (const bf16*)x, row_pair, num_tiles, (bf16*)xp, H, K, capacity_rows, row_scale);
   return b200_check_launch("b200_moe_gather");
+}
+
+extern "C" int b200_moe_gather(const void* x, const int32_t* row_pair, const int32_t* num_tiles, void* xp, int H,
+                               int K, int capacity_rows, void* stream) {
+  return b200_moe_gather_scaled(x, row_pair, num_tiles, xp, H, K, capacity_rows, nullptr, stream);
 }
 
 extern "C" int b200_moe_combine(const void* yp, const int32_t* pair_row, void* out, int T, int H, int K,

@@ -3,6 +3,8 @@
 //   moe_route_biased:  s = softmax(z) over all E router outputs (fp32 logits); the K outputs with the largest
 //                      s + correction are chosen (ties: the lowest index); their weights are
 //                      s / (sum of the chosen s + 1e-20) * scale -- the correction steers the choice only.
+//   moe_route_scored:  the same with two options: s = sigmoid(z) per output instead of the softmax, and weights that
+//                      are the chosen scores as they are (times scale), not renormalised.
 //   moe_combine_mixed: out[t] = sum_j ( id_j < n_real ? yp[pair_row[t K + j]] : w_j * x[t] ) (+ shared[t]).
 //                      Routed rows arrive already multiplied by their weight (the down projection's row
 //                      scale); an identity expert returns the layer input itself times the weight.  fp32 sum in a
@@ -26,7 +28,8 @@ __device__ __forceinline__ float rb_f32(bf16 v) { return __bfloat162float(v); }
 // one warp per token, lane l holds outputs l, l + 32, ...
 __global__ void __launch_bounds__(128)
 moe_route_biased_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction,
-                        int32_t* __restrict__ topk_ids, float* __restrict__ topk_w, int T, int E, int K, float scale) {
+                        int32_t* __restrict__ topk_ids, float* __restrict__ topk_w, int T, int E, int K, float scale,
+                        int sigmoid_scores, int renormalize) {
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   float s[kRbPerLane], c[kRbPerLane];
@@ -38,19 +41,31 @@ moe_route_biased_kernel(const float* __restrict__ logits, int64_t ld, const floa
     mx = fmaxf(mx, s[i]);
   }
   mx = warp_max(mx);
-  float sum = 0.f;
+  if (sigmoid_scores) {
+    // every output scored on its own; without a correction the choice is made on the logits themselves (the
+    // sigmoid is monotone, and two large logits must not tie where it saturates)
 #pragma unroll
-  for (int i = 0; i < kRbPerLane; ++i) {
-    const int e = lane + 32 * i;
-    s[i] = e < E ? expf(s[i] - mx) : 0.f;
-    sum += s[i];
-  }
-  const float inv = 1.0f / warp_sum(sum);
+    for (int i = 0; i < kRbPerLane; ++i) {
+      const int e = lane + 32 * i;
+      const float z = s[i];
+      s[i] = e < E ? 1.0f / (1.0f + expf(-z)) : 0.f;
+      c[i] = e < E ? (correction != nullptr ? s[i] + correction[e] : z) : -CUDART_INF_F;
+    }
+  } else {
+    float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < kRbPerLane; ++i) {
-    const int e = lane + 32 * i;
-    s[i] *= inv;
-    c[i] = e < E ? s[i] + (correction != nullptr ? correction[e] : 0.f) : -CUDART_INF_F;
+    for (int i = 0; i < kRbPerLane; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < E ? expf(s[i] - mx) : 0.f;
+      sum += s[i];
+    }
+    const float inv = 1.0f / warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < kRbPerLane; ++i) {
+      const int e = lane + 32 * i;
+      s[i] *= inv;
+      c[i] = e < E ? s[i] + (correction != nullptr ? correction[e] : 0.f) : -CUDART_INF_F;
+    }
   }
   float wsum = 0.f, mine_w = 0.f;
   int mine_id = 0;
@@ -77,7 +92,7 @@ moe_route_biased_kernel(const float* __restrict__ logits, int64_t ld, const floa
   }
   if (lane < K) {
     topk_ids[(size_t)t * K + lane] = mine_id;
-    topk_w[(size_t)t * K + lane] = mine_w / (wsum + 1e-20f) * scale;
+    topk_w[(size_t)t * K + lane] = (renormalize ? mine_w / (wsum + 1e-20f) : mine_w) * scale;
   }
 }
 
@@ -105,15 +120,21 @@ moe_combine_mixed_kernel(const TP* __restrict__ yp, int64_t ldp, const int32_t* 
 
 using namespace b200;
 
-extern "C" int b200_moe_route_biased(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids,
-                                     float* topk_w, int T, int E, int K, float scale, void* stream) {
+extern "C" int b200_moe_route_scored(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids,
+                                     float* topk_w, int T, int E, int K, float scale, int sigmoid_scores,
+                                     int renormalize, void* stream) {
   B200_REQUIRE(ld >= E, "moe_route_biased: row stride %lld < E=%d", (long long)ld, E);
   B200_REQUIRE(T >= 0 && E >= 1 && E <= 32 * kRbPerLane && K >= 1 && K <= kRbMaxTop && K <= E,
                "moe_route_biased: unsupported E=%d K=%d (E <= %d, K <= %d)", E, K, 32 * kRbPerLane, kRbMaxTop);
   if (T == 0) return B200_OK;
   moe_route_biased_kernel<<<(T + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits, ld, correction, topk_ids, topk_w, T, E, K,
-                                                                       scale);
+                                                                       scale, sigmoid_scores, renormalize);
   return b200_check_launch("b200_moe_route_biased");
+}
+
+extern "C" int b200_moe_route_biased(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids,
+                                     float* topk_w, int T, int E, int K, float scale, void* stream) {
+  return b200_moe_route_scored(logits, ld, correction, topk_ids, topk_w, T, E, K, scale, 0, 1, stream);
 }
 
 extern "C" int b200_moe_combine_mixed(const void* yp, int p_f32, int64_t ldp, const int32_t* pair_row,

@@ -1,0 +1,168 @@
+// Per-head preparation of queries, keys and values between a fused input projection and a mixer's core kernel:
+// the element-wise steps that different mixers combine, in one launch.
+//
+//   feature map   silu(x) on the head's entries (queries, keys and values alike), or none;
+//   rotation      the first `dims` entries of a query / key head are rotated by the angle position * freq[i] of
+//                 pair i -- pairs (2i, 2i+1) ("interleaved") or (i, i + dims/2) ("half"); the rest pass unchanged.
+//                 The angle is formed and reduced to [-pi, pi] in fp64, cos / sin of the remainder in fp32;
+//   unit norm     the rotated head over its root mean square, x / sqrt(mean(x^2) + eps), no weight;
+//   factor        a constant on the queries and one on the keys (after rotation and norm).
+//
+// Where the results go:
+//   queries       q_out rows (the projection itself = in place, or a separate fp32 buffer);
+//   keys, values  either the pages of a KV cache (K [blocks][G][page][dk], V [blocks][G][page][dv]) at slots[t]
+//                 (a softmax-attention mixer), or rows of a separate buffer (a recurrent mixer reads them once);
+//   values        come from their own columns, or are the keys AS PROJECTED (before feature map, rotation and
+//                 norm) when the mixer has no value projection.
+// One warp per (token, head slot): slots [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (absent when the
+// values are the keys).  Each lane keeps its entries in registers between the sum of squares and the store.
+// Source type TA (bf16 | fp32), destination type TD (the same, or fp32 for recurrent mixers).
+#include "common.cuh"
+#include "runtime.h"
+#include "../../include/b200.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float rp_f32(float v) { return v; }
+__device__ __forceinline__ float rp_f32(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void rp_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void rp_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int kRpWarps = 8, kRpPairs = 8, kRpTail = 16;     // rotated width <= 512, unrotated rest <= 512
+
+struct RotPrepArgs {
+  const void* proj;
+  int64_t ld;
+  int q_col, k_col, v_col;          // first column of the q / k / v heads in a projection row (v_col < 0: values are keys)
+  const int32_t* positions;
+  const int32_t* slots;             // cache slot of every token (cache destinations only)
+  void* q_out;
+  int64_t ldq;
+  void* k_out;                      // k_cache, or a row buffer with leading dimension ldk
+  int64_t ldk;
+  void* v_out;
+  int64_t ldv;
+  int paged;                        // 1: k_out / v_out are pages
+  int page;
+  int H, G, dk, dv;
+  int feature;                      // 0 none, 1 silu
+  int dims, half_layout;            // dims == 0: no rotation
+  const double* freq;
+  int unit_norm;
+  float eps, q_mul, k_mul;
+};
+
+template <typename TA, typename TD>
+__global__ void __launch_bounds__(kRpWarps * 32)
+rot_prep_kernel(RotPrepArgs a) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31;
+  const int hs = blockIdx.y * kRpWarps + (threadIdx.x >> 5);
+  const int H = a.H, G = a.G, dk = a.dk, dv = a.dv;
+  const bool has_v = a.v_col >= 0;
+  if (hs >= H + G + (has_v ? G : 0)) return;
+  const bool is_q = hs < H, is_k = !is_q && hs < H + G;
+  const int g = is_q ? hs : (is_k ? hs - H : hs - H - G);
+  const TA* src = reinterpret_cast<const TA*>(a.proj) + (size_t)t * a.ld +
+                  (is_q ? a.q_col + g * dk : (is_k ? a.k_col + g * dk : a.v_col + g * dv));
+  const int width = (is_q || is_k) ? dk : dv;
+  size_t cache_row = 0;
+  if (!is_q && a.paged) {
+    const int slot = a.slots[t];
+    if (slot < 0) return;
+    cache_row = ((size_t)(slot / a.page) * G + g) * a.page + (slot % a.page);
+  }
+  TD* dst;
+  if (is_q) dst = reinterpret_cast<TD*>(a.q_out) + (size_t)t * a.ldq + g * dk;
+  else if (is_k) dst = reinterpret_cast<TD*>(a.k_out) + (a.paged ? cache_row * dk : (size_t)t * a.ldk + g * dk);
+  else dst = reinterpret_cast<TD*>(a.v_out) + (a.paged ? cache_row * dv : (size_t)t * a.ldv + g * dv);
+
+  if (!is_q && !is_k) {             // a value head: feature map only
+    for (int d = lane; d < dv; d += 32) {
+      float x = rp_f32(src[d]);
+      if (a.feature == 1) x = x / (1.0f + expf(-x));
+      rp_store(dst + d, x);
+    }
+    return;
+  }
+  const int dims = a.dims, half = dims >> 1;
+  TD* vdst = nullptr;               // values are the keys as projected
+  if (is_k && !has_v && a.v_out != nullptr)
+    vdst = reinterpret_cast<TD*>(a.v_out) + (a.paged ? cache_row * dv : (size_t)t * a.ldv + g * dv);
+  float u[kRpPairs], v[kRpPairs], rest[kRpTail];
+  float ss = 0.f;
+  const int pos = a.positions[t];
+#pragma unroll
+  for (int i = 0; i < kRpPairs; ++i) {
+    const int j = lane + 32 * i;
+    u[i] = v[i] = 0.f;
+    if (j < half) {
+      const int d0 = a.half_layout ? j : 2 * j, d1 = a.half_layout ? j + half : 2 * j + 1;
+      float x0 = rp_f32(src[d0]), x1 = rp_f32(src[d1]);
+      if (vdst != nullptr) { rp_store(vdst + d0, x0); rp_store(vdst + d1, x1); }
+      if (a.feature == 1) { x0 = x0 / (1.0f + expf(-x0)); x1 = x1 / (1.0f + expf(-x1)); }
+      const double ang = (double)pos * a.freq[j];
+      const float rem = (float)(ang - 6.283185307179586 * rint(ang * 0.15915494309189535));
+      float sn, cs;
+      sincosf(rem, &sn, &cs);
+      u[i] = x0 * cs - x1 * sn;
+      v[i] = x1 * cs + x0 * sn;
+      ss = fmaf(u[i], u[i], fmaf(v[i], v[i], ss));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRpTail; ++i) {
+    const int d = dims + lane + 32 * i;
+    rest[i] = 0.f;
+    if (d < width) {
+      float x = rp_f32(src[d]);
+      if (vdst != nullptr) rp_store(vdst + d, x);
+      if (a.feature == 1) x = x / (1.0f + expf(-x));
+      rest[i] = x;
+      ss = fmaf(x, x, ss);
+    }
+  }
+  float mul = is_q ? a.q_mul : a.k_mul;
+  if (a.unit_norm) mul *= 1.0f / sqrtf(warp_sum(ss) / (float)width + a.eps);
+#pragma unroll
+  for (int i = 0; i < kRpPairs; ++i) {
+    const int j = lane + 32 * i;
+    if (j < half) {
+      rp_store(dst + (a.half_layout ? j : 2 * j), u[i] * mul);
+      rp_store(dst + (a.half_layout ? j + half : 2 * j + 1), v[i] * mul);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRpTail; ++i) {
+    const int d = dims + lane + 32 * i;
+    if (d < width) rp_store(dst + d, rest[i] * mul);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_col, int k_col, int v_col,
+                             const int32_t* positions, const int32_t* slots, void* q_out, int64_t ldq, void* k_out,
+                             int64_t ldk, void* v_out, int64_t ldv, int dst_f32, int paged, int page, int T, int H, int G,
+                             int dk, int dv, int feature, int dims, int half_layout, const double* freq, int unit_norm,
+                             float eps, float q_mul, float k_mul, void* stream) {
+  B200_REQUIRE(T >= 0 && H > 0 && G > 0 && dk > 0 && dv > 0, "rot_prep: bad shape");
+  B200_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= dk && dims <= 64 * kRpPairs && dk - dims <= 32 * kRpTail,
+               "rot_prep: %d rotated of %d entries (rotated <= %d, rest <= %d)", dims, dk, 64 * kRpPairs, 32 * kRpTail);
+  B200_REQUIRE(dims == 0 || (freq != nullptr && positions != nullptr), "rot_prep: a rotation needs frequencies and positions");
+  B200_REQUIRE(feature == 0 || feature == 1, "rot_prep: unknown feature map %d", feature);
+  B200_REQUIRE(!paged || (slots != nullptr && page > 0), "rot_prep: cache destinations need slots");
+  B200_REQUIRE(v_col >= 0 || v_out == nullptr || dv == dk, "rot_prep: values that are keys have the keys' width");
+  B200_REQUIRE(src_f32 ? dst_f32 : 1, "rot_prep: fp32 rows are not rounded to bf16 here");
+  if (T == 0) return B200_OK;
+  RotPrepArgs a{proj, ld, q_col, k_col, v_col, positions, slots, q_out, ldq, k_out, ldk, v_out, ldv, paged, page, H, G, dk, dv,
+                feature, dims, half_layout, freq, unit_norm, eps, q_mul, k_mul};
+  const int n_slots = H + G + (v_col >= 0 ? G : 0);
+  dim3 grid(T, (n_slots + kRpWarps - 1) / kRpWarps);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (src_f32) rot_prep_kernel<float, float><<<grid, kRpWarps * 32, 0, s>>>(a);
+  else if (dst_f32) rot_prep_kernel<bf16, float><<<grid, kRpWarps * 32, 0, s>>>(a);
+  else rot_prep_kernel<bf16, bf16><<<grid, kRpWarps * 32, 0, s>>>(a);
+  return b200_check_launch("b200_rot_prep");
+}

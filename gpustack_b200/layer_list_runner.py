@@ -1,4 +1,4 @@
-"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik, Danipel).
+"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik, Danipel, Resevik).
 
 Same step interface as runner.ModelRunner -- the engine, the scheduler's plans, the staging buffer, CUDA-graph
 decode steps and the sampler are shared -- with this family's layer sequence:
@@ -20,7 +20,19 @@ decode steps and the sampler are shared -- with this family's layer sequence:
                    cache (one shared row per token: G = 1, values = the first kv_rank entries of the key rows;
                    softmax sink optional) -> per-head W_uv -> output projection.
 
-Residual schemes (config.residual): "post_ln" as drawn above; "streams": pre-norm over S fp32 residual copies,
+  linear_attention mixer: rot_prep (feature map / rotation / key factor -> fp32 q | k | v rows) -> decayed
+                   linear-attention scan over every sequence's new rows (state slot in / out, fp32; chunk form for
+                   prompt portions) -> output norm (per head, or all heads with a weight) x sigmoid / SiLU gate.
+  attention mixer with rotation: rot_prep (rotation, weightless q / k norm, keys to their pages, values = the keys
+                   as projected) -> the same attention kernels, with a sliding window.
+
+Residual schemes (config.residual): "post_ln" as drawn above; "parallel": pre-norm with ONE RMS norm per layer,
+
+    embed * scale -> per layer run [ x += branches of the layer before (+ embedding before a repeated pass) ; h = RMSnorm(x)
+                                     -> mixer(h) and feed-forward(h) side by side ] -> x += last branches -> RMSnorm
+
+where a span of layers may run several times with the same weights (config.runs(): caches and state per run) and
+ONE add_rms_norm launch does the sum and the next norm; "streams": pre-norm over S fp32 residual copies,
 
     embed * scale -> S streams -> per sublayer [ u = sum_s in[s] x_s -> tanh norm -> sublayer ->
                                                  x_t <- sum_s mix[s,t] x_s + m out[t] y ]  -> sum of the streams -> tanh norm
@@ -71,6 +83,10 @@ class LayerListRunner(ModelRunner):
             raise B200Error("prefill tile sizes of the attention kernels do not nest")
         self._dec_ws = {}
         self.streams = cfg.residual == "streams"
+        self.parallel = cfg.residual == "parallel"
+        self.runs = cfg.runs()                 # [(layer, embedding added before it)]: caches and state belong to a run
+        self.looped = any(again for _, again in self.runs)
+        self.layer_trace = None                # a list: receives the fp32 residual after every layer run (tests, debugging)
         self.S = cfg.n_streams if self.streams else 1
         self.proj_width = max(lw.proj.shape[0] for lw in self.w.layers)
         self.mix_width = max(l.mixer.out_width for l in cfg.layers)
@@ -83,9 +99,11 @@ class LayerListRunner(ModelRunner):
         self.lat_o_width = max([m.heads * m.kv_rank for m in lat] or [0])
         self.routed = [l.mlp.moe for l in cfg.layers if l.mlp is not None and l.mlp.kind == "moe"]
         rec = [l.mixer for l in cfg.layers if l.mixer.kind == "mlstm"]
+        lin = [l.mixer for l in cfg.layers if l.mixer.kind == "linear_attention"]
         self.gate_width = max([2 * m.heads for m in rec] or [0])
-        self.rec_width = max([m.out_width for m in rec] or [0])
-        self.state: List[Optional[tuple]] = [None] * len(cfg.layers)
+        self.rec_width = max([m.out_width for m in rec + lin] or [0])
+        self.lin_width = max([2 * m.heads * m.dim + m.out_width for m in lin] or [0])
+        self.state: List[Optional[tuple]] = [None] * len(self.runs)
         self.num_state_slots = 0
 
     def _alloc_model_buffers(self):
@@ -100,6 +118,11 @@ class LayerListRunner(ModelRunner):
         self.act = e(T * max(1, self.ff_width), dt=a)
         self.gates = e(T * max(1, self.gate_width), dt=torch.float32)
         self.o_raw = e(T * max(1, self.rec_width), dt=torch.float32)
+        self.lin32 = e(T * max(1, self.lin_width), dt=torch.float32)   # prepared q | k | v rows of a linear-attention mixer
+        if self.parallel:
+            self.y2 = e(T, D, dt=torch.float32)           # the feed-forward's output beside the mixer's (self.y)
+            self.emb32 = e(T, D, dt=torch.float32) if self.looped else None   # the embedding output, added again per pass
+        self._pending = (None, None)                      # branch outputs not yet summed into the residual
         self.lat_q = e(T * max(1, self.lat_q_width), dt=a)        # queries of a mixer whose queries have a latent
         self.lat_cq = e(T * max(1, self.lat_q_rank), dt=a)        # the normed query latent
         self.lat_qa = e(T * max(1, self.lat_qa_width), dt=a)      # absorbed queries [H][kv_rank | rot_dim]
@@ -121,10 +144,10 @@ class LayerListRunner(ModelRunner):
         """Pages of every attention layer that owns keys and values; a `kv_from` layer aliases its owner's."""
         self.num_blocks = num_blocks
         cfg = self.mcfg
-        self.k_cache = [None] * len(cfg.layers)
-        self.v_cache = [None] * len(cfg.layers)
-        for l, layer in enumerate(cfg.layers):
-            m = layer.mixer
+        self.k_cache = [None] * len(self.runs)
+        self.v_cache = [None] * len(self.runs)
+        for l, (li, _) in enumerate(self.runs):          # one cache per RUN of a layer (a repeated span: one per pass)
+            m = cfg.layers[li].mixer
             if m.kind == "attention" and m.kv_from is None:
                 self.k_cache[l] = torch.zeros(num_blocks, m.kv_heads, self.block_size, m.dim, dtype=self.act_dtype,
                                               device=self.device)
@@ -135,9 +158,9 @@ class LayerListRunner(ModelRunner):
                 self.k_cache[l] = torch.zeros(num_blocks, 1, self.block_size, m.cache_width, dtype=self.act_dtype,
                                               device=self.device)
                 self.v_cache[l] = self.k_cache[l]
-        for l, layer in enumerate(cfg.layers):
-            m = layer.mixer
-            if m.kind == "attention" and m.kv_from is not None:
+        for l, (li, _) in enumerate(self.runs):
+            m = cfg.layers[li].mixer
+            if m.kind == "attention" and m.kv_from is not None:      # (designs with kv_from have no repeated span)
                 self.k_cache[l], self.v_cache[l] = self.k_cache[m.kv_from], self.v_cache[m.kv_from]
 
     def init_state(self, num_slots: int) -> None:
@@ -145,12 +168,14 @@ class LayerListRunner(ModelRunner):
         the slots out): S [slots, H, dv, dk] (key index fastest), and per 32-column slice of dv the normaliser n [slots, H, Z, dk]
         and the stabiliser m [slots, H, Z]."""
         self.num_state_slots = num_slots
-        for l, layer in enumerate(self.mcfg.layers):
-            m = layer.mixer
+        f = lambda *s: torch.zeros(*s, dtype=torch.float32, device=self.device)   # noqa: E731
+        for l, (li, _) in enumerate(self.runs):
+            m = self.mcfg.layers[li].mixer
+            if m.kind == "linear_attention":         # S [slots, H, dv, dk]
+                self.state[l] = (f(num_slots, m.heads, m.vdim, m.dim),)
             if m.kind != "mlstm":
                 continue
             z = ops.mlstm_state_slices(m.vdim)
-            f = lambda *s: torch.zeros(*s, dtype=torch.float32, device=self.device)   # noqa: E731
             self.state[l] = (f(num_slots, m.heads, m.vdim, m.dim), f(num_slots, m.heads, z, m.dim), f(num_slots, m.heads, z))
 
     def init_host_kv(self, slots: int) -> None:
@@ -168,8 +193,32 @@ class LayerListRunner(ModelRunner):
                              xb_out=self.xb[:T])
             self.stats["kernel_launches"] += 2
             return
+        if self.parallel:      # the first layer's norm reads the embedding output; a repeated span adds it again
+            ops.embed_streams(ids, self.w.embed, self.emb32[:T] if self.looped else self.resid32[:T], 1,
+                              self.mcfg.embed_scale)
+            self._pending = (None, None)
+            self.stats["kernel_launches"] += 1
+            return
         ops.embed_rows(ids, self.w.embed, self.resid32[:T], self.xb[:T])
         self.stats["kernel_launches"] += 1
+
+    def _open_layer(self, T: int, r: int, lw, again: bool) -> None:
+        """Parallel residual: the branch outputs of the layer before (and, before a repeated pass, the embedding
+        output) enter the fp32 stream, and this layer's ONE norm prepares self.xb for its mixer and feed-forward."""
+        a, b = self._pending
+        first = r == 0 and self.looped
+        ops.add_rms_norm(self.emb32[:T] if first else self.resid32[:T], lw.norm1, self.mcfg.norm_eps, a=a, b=b,
+                         c=self.emb32[:T] if again else None, x_out=self.resid32[:T], xb_out=self.xb[:T])
+        self._pending = (None, None)
+        self.stats["kernel_launches"] += 1
+
+    def _close_layer(self, T: int, has_ff: bool) -> None:
+        self._pending = (self.y[:T], self.y2[:T] if has_ff else None)
+        if self.layer_trace is not None:       # materialise the stream after this layer (not on the serving path)
+            ops.add_rms_norm(self.resid32[:T], None, self.mcfg.norm_eps, a=self._pending[0], b=self._pending[1],
+                             x_out=self.resid32[:T])
+            self._pending = (None, None)
+            self.layer_trace.append(self.resid32[:T].clone())
 
     def _join(self, T: int, l: int, q: int) -> None:
         """The branch output self.y of sublayer q (1 mixer, 2 feed-forward) of layer l enters the residual, and the
@@ -226,26 +275,38 @@ class LayerListRunner(ModelRunner):
         rows (lens_d / bt_d).  cu_all / ctx_all / slots_all list both kinds for the recurrent scan."""
         cfg, eps = self.mcfg, self.mcfg.norm_eps
         pos, slots = self._pos, self._slots
-        for l, (layer, lw) in enumerate(zip(cfg.layers, self.w.layers)):
+        for l, (li, again) in enumerate(self.runs):      # l indexes the run (caches, state), li the layer (weights)
+            layer, lw = cfg.layers[li], self.w.layers[li]
             m = layer.mixer
             proj = self._view(self.proj, T, lw.proj.shape[0])
             out = self._view(self.mix_out, T, m.out_width)
+            if self.parallel:
+                self._open_layer(T, l, lw, again)
             ops.linear(self.xb[:T], lw.proj, proj)
             if m.kind == "latent_attention":
                 self._latent_attention(l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d)
             elif m.kind == "attention":
                 own = m.kv_from is None
                 H, G, dk, dv = m.heads, m.kv_heads, m.dim, m.vdim
-                ops.attn_prep(proj, lw.proj_bias, lw.q_norm, lw.k_norm, pos, slots, self.k_cache[l] if own else None,
-                              self.v_cache[l] if own else None, H, G, dk, dv, eps, m.q_temp_coef, m.q_temp_every)
-                gate_col = (H * dk + (G * (dk + dv) if own else 0)) if m.gate else -1
+                if m.rot is not None or m.values_are_keys or m.qk_unit_norm:
+                    # rotation, then the weightless q / k norm; keys to their pages, values = the keys as projected
+                    ops.rot_prep(proj, 0, H * dk, -1 if m.values_are_keys else (H + G) * dk, pos, slots, proj,
+                                 self.k_cache[l], self.v_cache[l], H, G, dk, dv, paged=True,
+                                 rot_dims=m.rot.dims if m.rot is not None else 0,
+                                 half_layout=m.rot is not None and m.rot.layout == "half", freq=lw.rot_freq,
+                                 unit_norm=m.qk_unit_norm, eps=eps)
+                else:
+                    ops.attn_prep(proj, lw.proj_bias, lw.q_norm, lw.k_norm, pos, slots, self.k_cache[l] if own else None,
+                                  self.v_cache[l] if own else None, H, G, dk, dv, eps, m.q_temp_coef, m.q_temp_every)
+                kv_cols = 0 if not own else (G * dk if m.values_are_keys else G * (dk + dv))
+                gate_col = (H * dk + kv_cols) if m.gate else -1
                 kc, vc = self.k_cache[l], self.v_cache[l]
                 if nt and self.fast_prefill[l]:
                     ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, out[:Tp], H, G, dk,
                                               m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None)
                 elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
-                                          H, G, dk, dv, m.scale, tile_rows=self.prefill_tile)
+                                          H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window)
                 if Bd and self.fast_decode[l]:
                     splits, ws = self._decode_plan(Bd, m)
                     ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
@@ -253,8 +314,21 @@ class LayerListRunner(ModelRunner):
                                           gate=proj[Tp:T, gate_col:] if m.gate else None)
                 elif Bd:
                     ops.attn_sink_decode(proj[Tp:T], gate_col, kc, vc, bt_d, lens_d, lw.sink, out[Tp:T], H, G, dk, dv,
-                                         m.scale)
+                                         m.scale, window=m.window)
                 self.stats["kernel_launches"] += 2 + (1 if nt else 0) + (1 if Bd else 0)
+            elif m.kind == "linear_attention":
+                H, dk, dv = m.heads, m.dim, m.vdim
+                kc, vc = H * dk, 2 * H * dk
+                x32 = self._view(self.lin32, T, vc + H * dv)
+                # feature map / rotation / key factor in fp32: what enters the recurrence is never rounded to bf16
+                ops.rot_prep(proj, 0, kc, vc, pos, None, x32, x32[:, kc:], x32[:, vc:], H, H, dk, dv, paged=False,
+                             feature=m.feature, rot_dims=m.rot.dims if m.rot is not None else 0,
+                             half_layout=m.rot is not None and m.rot.layout == "half", freq=lw.rot_freq, k_mul=m.k_scale)
+                o_raw = self._view(self.o_raw, T, H * dv)
+                ops.linattn_scan(x32, 0, kc, vc, lw.decay, cu_all, ctx_all, slots_all, self.state[l][0], o_raw, H, dk, dv,
+                                 max_len=Tp if Tp else 1)
+                ops.linattn_out(o_raw, proj, vc + H * dv, lw.out_norm, out, H, dv, eps, m.out_norm == "all_heads", m.gate_act)
+                self.stats["kernel_launches"] += 4
             else:
                 H, dk, dv = m.heads, m.dim, m.vdim
                 gates = self._view(self.gates, T, 2 * H)
@@ -267,10 +341,15 @@ class LayerListRunner(ModelRunner):
                 self.stats["kernel_launches"] += 4
             ops.linear(out, lw.o, self.y[:T])
             self.stats["kernel_launches"] += 1
-            self._join(T, l, 1)
+            if self.parallel:      # the feed-forward reads the same normed rows; both outputs wait for the next norm
+                if layer.mlp is not None:
+                    self._feed_forward(T, layer.mlp, lw, self.y2[:T])
+                self._close_layer(T, layer.mlp is not None)
+                continue
+            self._join(T, li, 1)
             if layer.mlp is not None:
                 self._feed_forward(T, layer.mlp, lw)
-                self._join(T, l, 2)
+                self._join(T, li, 2)
 
     def _latent_attention(self, l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d) -> None:
         """Latent attention in the absorbed form: scores and values are taken straight from the cached latent rows,
@@ -304,8 +383,16 @@ class LayerListRunner(ModelRunner):
         ops.head_linear(o_lat, lw.uv, out, H, n=dv, k=R, x_head=R, out_head=dv)
         self.stats["kernel_launches"] += 3 + (1 if nt else 0) + (1 if Bd else 0)
 
-    def _feed_forward(self, T: int, mlp, lw) -> None:
-        """self.xb[:T] -> self.y[:T] (fp32)."""
+    def _feed_forward(self, T: int, mlp, lw, y=None) -> None:
+        """self.xb[:T] -> y (fp32; self.y[:T] unless given)."""
+        y = self.y[:T] if y is None else y
+        if mlp.kind == "moe" and mlp.moe.weight_on == "input":
+            e = mlp.moe
+            ops.routed_experts(self.xb[:T], lw.router, lw.correction, lw.w13, lw.w2, self.routed_ws, y, e.experts, 0, e.top,
+                               e.scale, e.ff, e.limit, sigmoid=e.score == "sigmoid", renormalize=e.renormalize,
+                               weight_on="input", act=e.act)
+            self.stats["kernel_launches"] += ops.ROUTED_LAUNCHES
+            return
         if mlp.kind == "moe":
             e = mlp.moe
             shared = None
@@ -315,7 +402,7 @@ class LayerListRunner(ModelRunner):
                 shared = self.routed_ws.shared[:T]
                 ops.linear(act, lw.shared2, shared)
                 self.stats["kernel_launches"] += 2
-            ops.routed_experts(self.xb[:T], lw.router, lw.correction, lw.w13, lw.w2, self.routed_ws, self.y[:T], e.experts,
+            ops.routed_experts(self.xb[:T], lw.router, lw.correction, lw.w13, lw.w2, self.routed_ws, y, e.experts,
                                e.identity, e.top, e.scale, e.ff, e.limit, shared=shared)
             self.stats["kernel_launches"] += ops.ROUTED_LAUNCHES
             return
@@ -324,7 +411,7 @@ class LayerListRunner(ModelRunner):
             ops.linear(self.xb[:T], lw.up, act, relu2=True)            # squared ReLU in the GEMM's epilogue
         else:
             ops.gated_linear(self.xb[:T], lw.gate_up, act, mlp.act)
-        ops.linear(act, lw.down, self.y[:T])
+        ops.linear(act, lw.down, y)
         self.stats["kernel_launches"] += 2
 
     def _forward_decode(self, ids, B: int, bt, lens, state_slots) -> None:
@@ -346,7 +433,10 @@ class LayerListRunner(ModelRunner):
         cfg = self.mcfg
         if rows is None:
             rows = self.arange_dev[:n]
-        if self.streams:       # sum of the streams, tanh norm
+        if self.parallel:      # the last layer's branch outputs enter the sum here, for the wanted rows only
+            a, b = self._pending
+            ops.add_rms_norm(self.resid32, self.w.final_norm, cfg.norm_eps, a=a, b=b, rows=rows, xb_out=self.x_last[:n])
+        elif self.streams:       # sum of the streams, tanh norm
             ops.streams_step(self.resid32, self.S, rows=rows, xb_out=self.x_last[:n],
                              norm=(self.w.final_norm_alpha, self.w.final_norm, self.w.final_norm_b))
         else:

@@ -113,6 +113,19 @@ SIGNATURES = {
     "b200_moe_route_biased": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
     "b200_moe_combine_mixed": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _i64, _i32, _i32,
                                       _i32, _i32, _vp]),
+    "b200_add_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "b200_rot_prep": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i32, _i32, _i32,
+                             _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _f32, _vp]),
+    "b200_linattn_scan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200_linattn_out": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200_attn_sink_prefill_ex": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp,
+                                         _i64, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _i32, _vp]),
+    "b200_attn_sink_decode_ex": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
+                                        _i32, _i32, _i32, _f32, _i64, _i32, _vp]),
+    "b200_moe_route_scored": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _i32, _vp]),
+    "b200_linear_simt_grouped_ex": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i64, _i64,
+                                           _i64, _vp, _i32, _vp, _vp, _i32, _i64, _vp, _i32, _f32, _i32, _vp]),
+    "b200_moe_gather_scaled": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_mlstm_out": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
 }
 

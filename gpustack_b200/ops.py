@@ -527,29 +527,29 @@ def attn_sink_prefill_tile() -> int:
 
 
 def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out,
-                      H, G, dk, dv, scale, tile_rows: int = 0, v_ld: int = 0):
+                      H, G, dk, dv, scale, tile_rows: int = 0, v_ld: int = 0, window: int = 0):
     """v_ld: elements between value rows (0 = dv); v_cache is k_cache and v_ld == dk when the values are the
-    first dv entries of the key rows (a latent cache)."""
+    first dv entries of the key rows (a latent cache).  window > 0: position i sees j with 0 <= i - j < window."""
     _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_prefill: projection, cache and output must share one element type")
-    check(load().b200_attn_sink_prefill(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
-                                        _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
-                                        _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
-                                        _p(out), out.stride(0), H, G, dk, dv,
-                                        k_cache.shape[2], scale, v_ld, _stream()), "attn_sink_prefill")
+    check(load().b200_attn_sink_prefill_ex(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                           _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
+                                           _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
+                                           _p(out), out.stride(0), H, G, dk, dv,
+                                           k_cache.shape[2], scale, v_ld, int(window), _stream()), "attn_sink_prefill")
     return out
 
 
 def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale,
-                     v_ld: int = 0):
+                     v_ld: int = 0, window: int = 0):
     _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_decode: projection, cache and output must share one element type")
-    check(load().b200_attn_sink_decode(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
-                                       _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
-                                       _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, _stream()),
-          "attn_sink_decode")
+    check(load().b200_attn_sink_decode_ex(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                          _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
+                                          _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, int(window),
+                                          _stream()), "attn_sink_decode")
     return out
 
 
@@ -572,6 +572,60 @@ def mlstm_out(o_raw, proj, gate_col, norm_w, out, H, dv, eps):
     _cuda(o_raw, proj, norm_w, out)
     check(load().b200_mlstm_out(_p(o_raw), _p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(norm_w), _p(out),
                                 out.stride(0), o_raw.shape[0], H, dv, eps, _stream()), "mlstm_out")
+    return out
+
+
+# ------------------------------------------- pre-norm fp32 residual, rotation prep, decayed linear attention
+def add_rms_norm(x_in, w, eps: float, a=None, b=None, c=None, x_out=None, xb_out=None, rows=None):
+    """z = x_in + a + b + c (fp32 rows, addends optional); x_out = z; xb_out = RMSnorm(z) * w (bf16 or fp32).
+    rows: gather -- row r reads source row rows[r] and only xb_out is written.  w None: the sum alone."""
+    _cuda(x_in, a, b, c, w, x_out, xb_out, rows)
+    for t_, n_ in ((x_in, "x_in"), (a, "a"), (b, "b"), (c, "c"), (x_out, "x_out")):
+        if t_ is not None:
+            _req(t_, torch.float32, n_)
+    D = x_in.shape[1]
+    T = rows.shape[0] if rows is not None else (xb_out if xb_out is not None else x_out).shape[0]
+    check(load().b200_add_rms_norm_f32(_p(x_in), _p(a), _p(b), _p(c), _p(rows), _p(w), _p(x_out), _p(xb_out),
+                                       0 if xb_out is None else _is_f32(xb_out), T, D, eps, _stream()), "add_rms_norm")
+
+
+def rot_prep(proj, q_col: int, k_col: int, v_col: int, positions, slots, q_out, k_out, v_out, H, G, dk, dv, *,
+             paged: bool, feature: Optional[str] = None, rot_dims: int = 0, half_layout: bool = False, freq=None,
+             unit_norm: bool = False, eps: float = 0.0, q_mul: float = 1.0, k_mul: float = 1.0):
+    """Per-head feature map / rotation / unit norm / factor of a fused projection's q, k (and v) heads
+    (csrc/rot_prep.cu).  paged: k_out / v_out are cache pages [blocks, G, page, width] written at slots[t]; otherwise
+    row buffers.  v_col < 0: the values are the keys as projected."""
+    _cuda(proj, positions, slots, q_out, k_out, v_out, freq)
+    if freq is not None:
+        _req(freq, torch.float64, "freq")
+    dst = q_out if q_out is not None else k_out
+    if any(t_ is not None and t_.dtype != dst.dtype for t_ in (q_out, k_out, v_out)):
+        raise B200Error("rot_prep: one destination element type")
+    page = k_out.shape[2] if paged else 0
+    check(load().b200_rot_prep(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(positions), _p(slots),
+                               _p(q_out), q_out.stride(0), _p(k_out), 0 if paged else k_out.stride(0), _p(v_out),
+                               0 if (paged or v_out is None) else v_out.stride(0), _is_f32(dst), 1 if paged else 0, page,
+                               proj.shape[0], H, G, dk, dv, {None: 0, "silu": 1}[feature], rot_dims, 1 if half_layout else 0,
+                               _p(freq), 1 if unit_norm else 0, eps, q_mul, k_mul, _stream()), "rot_prep")
+
+
+def linattn_scan(x, q_col: int, k_col: int, v_col: int, decay, cu_seq, ctx_lens, state_slots, S, o_raw, H, dk, dv,
+                 max_len: int = 1):
+    """Decayed linear attention over every sequence's new rows of the fp32 rows x (state slot in, state slot out).
+    max_len: an upper bound of the new rows per sequence (prompt portions run in the chunk form)."""
+    _cuda(x, decay, cu_seq, ctx_lens, state_slots, S, o_raw)
+    _req(x, torch.float32, "x"); _req(S, torch.float32, "S"); _req(o_raw, torch.float32, "o_raw")
+    _req(decay, torch.float32, "decay")
+    check(load().b200_linattn_scan(_p(x), x.stride(0), q_col, k_col, v_col, _p(decay), _p(cu_seq), _p(ctx_lens),
+                                   _p(state_slots), _p(S), _p(o_raw), state_slots.shape[0], H, dk, dv, int(max_len),
+                                   _stream()), "linattn_scan")
+
+
+def linattn_out(o_raw, proj, gate_col: int, norm_w, out, H, dv, eps: float, all_heads: bool, gate_act: str):
+    _cuda(o_raw, proj, norm_w, out)
+    check(load().b200_linattn_out(_p(o_raw), _p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(norm_w), _p(out),
+                                  out.stride(0), o_raw.shape[0], H, dv, 1 if all_heads else 0,
+                                  {"sigmoid": 0, "silu": 1}[gate_act], eps, _stream()), "linattn_out")
     return out
 
 
@@ -763,16 +817,22 @@ class RoutedWorkspace:
 
 
 ROUTED_LAUNCHES = 6
+TC_GROUPED_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
 
 def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_real: int, n_identity: int, top_k: int,
-                   scale: float, ff: int, limit: float, shared=None):
+                   scale: float, ff: int, limit: float, shared=None, sigmoid: bool = False, renormalize: bool = True,
+                   weight_on: str = "output", act: str = "clamped_swish"):
     """out[t] (fp32) = sum over the top_k chosen router outputs of weight * expert(x[t]) (identity experts return
     x[t]) + shared[t].  router [n_real + n_identity, D]; w13 [n_real * 2 ff, D] interleaved; w2 [n_real * D, ff];
-    shared: the shared expert's output rows (fp32) or None.  Six launches, no host synchronisation."""
+    shared: the shared expert's output rows (fp32) or None.  Six launches, no host synchronisation.
+    sigmoid / renormalize: how the router scores and weights are formed (moe_biased.cu); weight_on "input": the sum
+    is over expert(weight * x[t]) -- the weight scales the gathered input row (tensor cores) or the accumulators before
+    the activation (CUDA cores) and the output rows are not scaled; act: the experts' gate activation."""
     T, D = x.shape
     E = n_real + n_identity
     n_pairs = T * top_k
+    act_name = act
     # tensor cores when both expert products fit the grouped tcgen05 GEMM (bf16, K multiples of 64, 256-row weight pairs)
     tc = (LAYER_LIST_TC and x.dtype == torch.bfloat16 and n_real > 0 and D % 256 == 0 and ff % 128 == 0 and x.is_contiguous()
           and w13.stride(0) == D and w2.stride(0) == ff)
@@ -784,25 +844,34 @@ def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_r
     lg = ws.logits[:T]
     # fp32 logits; a router padded to whole weight tiles (weights.load_layer_list) takes the tensor-core GEMM in bf16
     linear(x, router, lg, force_simt=router.shape[0] % 128 != 0)
-    moe_route_biased(lg, correction, top_k, scale, ws.topk_ids, ws.topk_w, E)
+    w_in = weight_on == "input"
+    if w_in and n_identity:
+        raise B200Error("routed_experts: identity experts with input weights are not defined")
+    check(L.b200_moe_route_scored(_p(lg), lg.stride(0), _p(correction), _p(ws.topk_ids), _p(ws.topk_w), T, E, top_k, scale,
+                                  1 if sigmoid else 0, 1 if renormalize else 0, st), "moe_route_scored")
     check(L.b200_moe_align(_p(ws.topk_ids), _p(ws.topk_w), n_pairs, E, bx, cap, _p(ws.pair_row), _p(ws.row_pair),
                            _p(ws.row_weight), _p(ws.tile_expert), _p(ws.num_tiles), st), "moe_align")
     act = ws.act[:cap * ff].view(cap, ff)
     if tc:
         if ws.xp is None:
             ws.xp = torch.empty(ws.capacity, D, dtype=torch.bfloat16, device=x.device)
-        check(L.b200_moe_gather(_p(x), _p(ws.row_pair), _p(ws.num_tiles), _p(ws.xp), D, top_k, cap, st), "moe_gather")
+        check(L.b200_moe_gather_scaled(_p(x), _p(ws.row_pair), _p(ws.num_tiles), _p(ws.xp), D, top_k, cap,
+                                       _p(ws.row_weight) if w_in else None, st), "moe_gather")
         check(L.b200_moe_grouped_gemm_ex(_p(ws.xp), _p(w13), _p(act), cap, 2 * ff, D, n_real, D, D, ff, None,
-                                         _p(ws.tile_expert), _p(ws.num_tiles), bx, 1, TC_GATED_ACTS["clamped_swish"], limit, 0,
+                                         _p(ws.tile_expert), _p(ws.num_tiles), bx, 1, TC_GROUPED_ACTS[act_name], limit, 0,
                                          st), "moe_grouped_gemm(gate_up)")
-        check(L.b200_moe_grouped_gemm_ex(_p(act), _p(w2), _p(ws.yp), cap, D, ff, n_real, ff, ff, D, _p(ws.row_weight),
+        check(L.b200_moe_grouped_gemm_ex(_p(act), _p(w2), _p(ws.yp), cap, D, ff, n_real, ff, ff, D,
+                                         None if w_in else _p(ws.row_weight),
                                          _p(ws.tile_expert), _p(ws.num_tiles), bx, 0, 0, 0.0, 1, st), "moe_grouped_gemm(down)")
     elif n_real:
-        linear_simt_grouped(x, w13, act, cap, ff, D, x.stride(0), w13.stride(0), ff, row_pair=ws.row_pair, top_k=top_k,
-                            tile_expert=ws.tile_expert, num_tiles=ws.num_tiles, n_real=n_real, w_expert=2 * ff * w13.stride(0),
-                            act=GATED_ACTS["clamped_swish"], limit=limit)
+        check(L.b200_linear_simt_grouped_ex(_p(x), _is_f32(x), _p(w13), _p(act), _is_f32(act), cap, ff, D, x.stride(0),
+                                            w13.stride(0), ff, 1, 0, 0, 0, _p(ws.row_pair), top_k, _p(ws.tile_expert),
+                                            _p(ws.num_tiles), n_real, 2 * ff * w13.stride(0),
+                                            _p(ws.row_weight) if w_in else None, GATED_ACTS[act_name], limit, 1 if w_in else 0,
+                                            st), "linear_simt_grouped(gate_up)")
         linear_simt_grouped(act, w2, ws.yp, cap, D, ff, ff, w2.stride(0), D, tile_expert=ws.tile_expert,
-                            num_tiles=ws.num_tiles, n_real=n_real, w_expert=D * w2.stride(0), row_scale=ws.row_weight)
+                            num_tiles=ws.num_tiles, n_real=n_real, w_expert=D * w2.stride(0),
+                            row_scale=None if w_in else ws.row_weight)
     check(L.b200_moe_combine_mixed(_p(ws.yp), 1, D, _p(ws.pair_row), _p(ws.topk_ids), _p(ws.topk_w), _p(x), _is_f32(x),
                                    x.stride(0), _p(shared), 0 if shared is None else shared.stride(0), _p(out), out.stride(0),
                                    T, D, top_k, n_real, st), "moe_combine_mixed")

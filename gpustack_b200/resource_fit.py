@@ -51,12 +51,15 @@ def _layer_list_workspace(m, e: EngineConfig) -> int:
     """Mirror of LayerListRunner._alloc_model_buffers / _alloc_step_io plus the recurrent state of every slot."""
     T, S, D = max(e.max_num_batched_tokens, e.max_num_seqs), e.max_num_seqs, m.hidden_size
     a = 4 if e.dtype == "float32" else 2
-    proj = mix = ff = gates = rec = lat = routed = 0
+    proj = mix = ff = gates = rec = lat = routed = lin = 0
     for l in m.layers:
         x = l.mixer
         if x.kind == "attention":
-            kv = 0 if x.kv_from is not None else x.kv_heads * (x.dim + x.vdim)
+            kv = 0 if x.kv_from is not None else x.kv_heads * (x.dim + (0 if x.values_are_keys else x.vdim))
             proj = max(proj, x.q_width + kv + (x.out_width if x.gate else 0))
+        elif x.kind == "linear_attention":
+            proj = max(proj, x.proj_rows)
+            rec, lin = max(rec, x.out_width), max(lin, 2 * x.heads * x.dim + x.out_width)
         elif x.kind == "latent_attention":
             proj = max(proj, x.proj_rows)
             lat = max(lat, (x.q_width + x.q_rank if x.q_rank else 0) + x.heads * (x.cache_width + x.kv_rank))
@@ -72,7 +75,8 @@ def _layer_list_workspace(m, e: EngineConfig) -> int:
         elif l.mlp is not None:
             ff = max(ff, l.mlp.ff)
     S_smp = min(T, max(S, e.max_logit_rows or 0))
-    act = T * (D * (4 * getattr(m, "n_streams", 1) + a + 4) + (proj + mix + ff + lat) * a + (gates + rec) * 4) + routed
+    par = 4 * (1 + (1 if m.loop_times > 1 else 0)) if m.residual == "parallel" else 0    # second branch output, embedding copy
+    act = T * (D * (4 * getattr(m, "n_streams", 1) + a + 4 + par) + (proj + mix + ff + lat) * a + (gates + rec + lin) * 4) + routed
     max_len = e.max_model_len or m.max_position_embeddings
     staging = (3 * T + 10 * S + 3 * S_smp + S * math.ceil(max_len / e.block_size) + 2 * T) * 4
     return act + S_smp * (D * a + m.vocab_size * 4) + staging + S * m.state_bytes_per_seq()

@@ -336,7 +336,9 @@ class LayerListLayer:
     """One layer of a layer-list decoder.  Everything that reads the mixer's input is ONE fused projection:
     attention  rows = [q: H*dk | k: G*dk | v: G*dv | gate: H*dv]   (no k / v rows with kv_from),
     mlstm      rows = [q: H*dk | k: H*dk | v: H*dv | gate: H*dv];  its two per-head gate projections are a
-    second, fp32-output projection `gates` = [input: H | forget: H]."""
+    second, fp32-output projection `gates` = [input: H | forget: H],
+    linear attention  rows = [q: H*dk | k: H*dk | v: H*dv | gate: H*dv]; an attention mixer whose values are its
+    keys has no v rows."""
     norm1: torch.Tensor
     proj: torch.Tensor
     o: torch.Tensor
@@ -366,6 +368,7 @@ class LayerListLayer:
     uv: Optional[torch.Tensor] = None            # [H*vdim, kv_rank]
     rot_freq: Optional[torch.Tensor] = None      # fp64 [dims/2]: angular frequency of every rotated pair
     rot_mag: float = 1.0                         # factor on cos and sin (frequency-scaled rotations)
+    decay: Optional[torch.Tensor] = None         # linear attention: fp32 [H], the per-head decay
     # gated feed-forward: gate_up rows interleaved (2i = gate_i, 2i+1 = up_i), `up` above is unused
     gate_up: Optional[torch.Tensor] = None       # [2 ff, D]
     # routed feed-forward
@@ -395,6 +398,7 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
     shapes: Dict[str, tuple] = {"embed": (cfg.vocab_size, D), "final.norm": (D,), "head": (cfg.vocab_size, D)}
     tanh = getattr(cfg, "norm", "layernorm") == "tanh"
     S = getattr(cfg, "streams", 0)
+    parallel = getattr(cfg, "residual", "post_ln") == "parallel"     # one norm per layer feeds both sublayers
 
     def norm_shapes(name):
         shapes[name] = (D,)
@@ -429,7 +433,8 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
                 shapes[p + "mix.q.norm"] = (m.dim,)
             if m.kv_from is None:
                 shapes[p + "mix.k"] = (m.kv_heads * m.dim, D)
-                shapes[p + "mix.v"] = (m.kv_heads * m.vdim, D)
+                if not m.values_are_keys:
+                    shapes[p + "mix.v"] = (m.kv_heads * m.vdim, D)
                 if m.qkv_bias:
                     shapes[p + "mix.k.b"] = (m.kv_heads * m.dim,)
                     shapes[p + "mix.v.b"] = (m.kv_heads * m.vdim,)
@@ -440,6 +445,12 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
             if m.gate:
                 shapes[p + "mix.g"] = (m.out_width, D)
             shapes[p + "mix.o"] = (D, m.out_width)
+        elif m.kind == "linear_attention":
+            for n, rows in (("q", m.heads * m.dim), ("k", m.heads * m.dim), ("v", m.out_width), ("g", m.out_width)):
+                shapes[p + "mix." + n] = (rows, D)
+            shapes[p + "mix.o"] = (D, m.out_width)
+            if m.out_norm == "all_heads":
+                shapes[p + "mix.norm"] = (m.out_width,)
         else:
             for n, rows in (("q", m.heads * m.dim), ("k", m.heads * m.dim), ("v", m.out_width), ("g", m.out_width)):
                 shapes[p + "mix." + n] = (rows, D)
@@ -449,14 +460,16 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
                 shapes[p + "mix." + n] = (m.heads, D)
                 shapes[p + "mix." + n + ".b"] = (m.heads,)
         if layer.mlp is not None:
-            norm_shapes(p + "norm2")
+            if not parallel:
+                norm_shapes(p + "norm2")
             if layer.mlp.kind == "moe":
                 e = layer.mlp.moe
                 for i in range(e.experts):
                     shapes[p + f"mlp.e{i}.gate"] = shapes[p + f"mlp.e{i}.up"] = (e.ff, D)
                     shapes[p + f"mlp.e{i}.down"] = (D, e.ff)
                 shapes[p + "mlp.router"] = (e.experts + e.identity, D)
-                shapes[p + "mlp.correction"] = (e.experts + e.identity,)
+                if e.score == "softmax":
+                    shapes[p + "mlp.correction"] = (e.experts + e.identity,)
                 if e.shared_ff:
                     shapes[p + "mlp.shared.gate"] = shapes[p + "mlp.shared.up"] = (e.shared_ff, D)
                     shapes[p + "mlp.shared.down"] = (D, e.shared_ff)
@@ -492,6 +505,7 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
 
     tanh = getattr(cfg, "norm", "layernorm") == "tanh"
     S = getattr(cfg, "streams", 0)
+    parallel = getattr(cfg, "residual", "post_ln") == "parallel"
 
     def hyper(prefix: str) -> torch.Tensor:
         if not S:        # one plain residual stream: read it, keep it, add the branch
@@ -516,7 +530,7 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
             lw.rot_freq, lw.rot_mag = torch.tensor(list(freqs), dtype=torch.float64).to(device), float(mag)
         elif m.kind == "attention":
             own = m.kv_from is None
-            names = ["q"] + (["k", "v"] if own else []) + (["g"] if m.gate else [])
+            names = ["q"] + ((["k"] if m.values_are_keys else ["k", "v"]) if own else []) + (["g"] if m.gate else [])
             lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in names]), o=g(p + "mix.o"))
             if m.qkv_bias:
                 lw.proj_bias = cat([p + f"mix.{n}.b" for n in (["q", "k", "v"] if own else ["q"])])
@@ -525,6 +539,15 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
                 lw.k_norm = g(p + "mix.k.norm") if own else None
             if m.sink:
                 lw.sink = g(p + "mix.sink").to(torch.float32).contiguous()
+            if m.rot is not None:
+                lw.rot_freq = torch.tensor(list(m.rot.frequencies()[0]), dtype=torch.float64).to(device)
+        elif m.kind == "linear_attention":
+            lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in "qkvg"]), o=g(p + "mix.o"))
+            if m.out_norm == "all_heads":
+                lw.out_norm = g(p + "mix.norm")
+            lw.decay = torch.tensor(list(m.decay), dtype=torch.float32).to(device)
+            if m.rot is not None:
+                lw.rot_freq = torch.tensor(list(m.rot.frequencies()[0]), dtype=torch.float64).to(device)
         else:
             lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in "qkvg"]), o=g(p + "mix.o"),
                                 gates=cat([p + "mix.i", p + "mix.f"]), gate_bias=cat([p + "mix.i.b", p + "mix.f.b"]),
@@ -534,7 +557,8 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
         if getattr(cfg, "residual", "post_ln") == "streams":
             lw.hc1 = hyper(p + "hc1")
         if layer.mlp is not None:
-            lw.norm2 = g(p + "norm2")
+            if not parallel:
+                lw.norm2 = g(p + "norm2")
             if tanh:
                 lw.norm2_b, lw.norm2_alpha = g(p + "norm2.b"), f32(p + "norm2.alpha")
             if getattr(cfg, "residual", "post_ln") == "streams":
@@ -545,7 +569,7 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
                 router = g(p + "mlp.router")
                 lw.router = torch.zeros(-(-router.shape[0] // 128) * 128, router.shape[1], dtype=BF16, device=device)
                 lw.router[:router.shape[0]] = router
-                lw.correction = f32(p + "mlp.correction")
+                lw.correction = f32(p + "mlp.correction") if e.score == "softmax" else None
                 lw.w13 = torch.cat([_interleave_rows(g(p + f"mlp.e{i}.gate"), g(p + f"mlp.e{i}.up"))
                                     for i in range(e.experts)], dim=0).contiguous()
                 lw.w2 = torch.cat([g(p + f"mlp.e{i}.down") for i in range(e.experts)], dim=0).contiguous()

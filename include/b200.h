@@ -376,6 +376,52 @@ int b200_moe_combine_mixed(const void* yp, int p_f32, int64_t ldp, const int32_t
                            const float* topk_w, const void* x, int x_f32, int64_t ldx, const void* shared, int64_t lds,
                            float* out, int64_t ldo, int T, int D, int K, int n_real, void* stream);
 
+/* ---- pre-norm fp32 residual, per-head preparation with rotation, decayed linear attention ---------------------- */
+/* z = x_in + a + b + c (a, b, c optional fp32 rows); x_out = z; xb_out = z / sqrt(mean(z^2) + eps) * w (bf16 or fp32).
+ * rows != NULL: gather (row r reads source row rows[r]; x_out must be NULL).  w == NULL: the sum only. */
+int b200_add_rms_norm_f32(const float* x_in, const float* a, const float* b, const float* c, const int32_t* rows,
+                          const void* w, float* x_out, void* xb_out, int xb_f32, int T, int D, float eps, void* stream);
+/* Per (token, head): feature map (0 none, 1 silu), rotation of the first `dims` entries (pairs (2i, 2i+1) or,
+ * half_layout, (i, i + dims/2); angle position * freq[i], fp64 freq), unit RMS norm (no weight), factors q_mul / k_mul.
+ * Queries to q_out rows; keys / values to cache pages at slots[t] (paged) or to row buffers; v_col < 0: the values
+ * are the keys as projected (written to v_out when it is not NULL).  src bf16 | fp32, dst the same or fp32. */
+int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_col, int k_col, int v_col, const int32_t* positions,
+                  const int32_t* slots, void* q_out, int64_t ldq, void* k_out, int64_t ldk, void* v_out, int64_t ldv,
+                  int dst_f32, int paged, int page, int T, int H, int G, int dk, int dv, int feature, int dims,
+                  int half_layout, const double* freq, int unit_norm, float eps, float q_mul, float k_mul, void* stream);
+/* S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over every sequence's new rows [cu_seq[s], cu_seq[s+1]) of the fp32
+ * rows x (q / k / v at their columns); state S [slots][H][dv][dk] fp32 in and out, zero start when ctx_lens[s] == 0;
+ * o_raw [T][H*dv] fp32.  max_len: an upper bound of the new rows per sequence (> 2: the chunk form). */
+int b200_linattn_scan(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* decay,
+                      const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S, float* o_raw,
+                      int n_seqs, int H, int dk, int dv, int max_len, void* stream);
+/* out = o_raw / rms * (w) * act(gate): all_heads: one RMS over the H*dv entries and w [H*dv]; else per head, w [dv] or
+ * NULL.  gate = proj[t, gate_col : gate_col + H*dv]; gate_act 0 sigmoid, 1 silu. */
+int b200_linattn_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col, const void* w, void* out,
+                     int64_t ldo, int T, int H, int dv, int all_heads, int gate_act, float eps, void* stream);
+/* The generic attention kernels with a sliding window (position i sees j with 0 <= i - j < window; 0 = none). */
+int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                              const void* v_cache, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                              const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles,
+                              int tile_rows, const float* sink, void* out, int64_t ldo, int H, int G, int dk, int dv,
+                              int page, float scale, int64_t v_ld, int window, void* stream);
+int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache, const void* v_cache,
+                             const int32_t* block_table, int max_blocks, const int32_t* seq_lens, int B, const float* sink,
+                             void* out, int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                             int window, void* stream);
+/* b200_moe_route_biased with sigmoid scores (sigmoid_scores != 0) and / or weights that are not renormalised. */
+int b200_moe_route_scored(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids, float* topk_w, int T,
+                          int E, int K, float scale, int sigmoid_scores, int renormalize, void* stream);
+/* b200_linear_simt_grouped whose row_scale multiplies the rows' input (before the activation) when scale_in != 0. */
+int b200_linear_simt_grouped_ex(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,
+                                int64_t ldx, int64_t ldw, int64_t ldy, int batch, int64_t bsx, int64_t bsw, int64_t bsy,
+                                const int32_t* row_pair, int top_k, const int32_t* tile_expert, const int32_t* num_tiles,
+                                int n_real, int64_t w_expert, const float* row_scale, int act, float limit, int scale_in,
+                                void* stream);
+/* b200_moe_gather whose gathered rows are multiplied by row_scale[row] (fp32 product, one rounding). */
+int b200_moe_gather_scaled(const void* x, const int32_t* row_pair, const int32_t* num_tiles, void* xp, int H, int K,
+                           int capacity_rows, const float* row_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
