@@ -301,13 +301,13 @@ class LayerListRunner(ModelRunner):
                 kv_cols = 0 if not own else (G * dk if m.values_are_keys else G * (dk + dv))
                 gate_col = (H * dk + kv_cols) if m.gate else -1
                 kc, vc = self.k_cache[l], self.v_cache[l]
-                if nt and self.fast_prefill[l]:
+                if nt and self.fast_prefill[li]:
                     ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, out[:Tp], H, G, dk,
                                               m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None)
                 elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
                                           H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window)
-                if Bd and self.fast_decode[l]:
+                if Bd and self.fast_decode[li]:
                     splits, ws = self._decode_plan(Bd, m)
                     ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
                                           num_splits=splits, workspace=ws, sink=lw.sink,
