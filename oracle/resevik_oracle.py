@@ -199,5 +199,46 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.flo
     return rms_norm(x, W["final.norm"], eps) @ W["head"].T
 
 
-def sqrt_dim(d: int) -> float:
-    return math.sqrt(d)
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Checkpoint tensor names and shapes (linear weights are [out, in])."""
+    D, V = int(cfg["width"]), int(cfg["vocab"])
+    out: Dict[str, tuple] = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    for l, layer in enumerate(cfg["layers"]):
+        p, mx = f"l{l}.", layer["mixer"]
+        H, dk = int(mx["heads"]), int(mx["dim"])
+        out[p + "norm1"] = (D,)
+        if layer["type"] == "attention":
+            out[p + "mix.q"], out[p + "mix.k"] = (H * dk, D), (int(mx["kv_heads"]) * dk, D)
+            out[p + "mix.o"] = (D, H * dk)
+        else:
+            dv = int(mx["vdim"])
+            out[p + "mix.q"] = out[p + "mix.k"] = (H * dk, D)
+            out[p + "mix.v"] = out[p + "mix.g"] = (H * dv, D)
+            out[p + "mix.o"] = (D, H * dv)
+            if layer["type"] == "lightning":
+                out[p + "mix.norm"] = (H * dv,)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            ff = int(mlp["expert"]["ff"])
+            for e in range(int(mlp["router"]["experts"])):
+                out[p + f"mlp.e{e}.gate"] = out[p + f"mlp.e{e}.up"] = (ff, D)
+                out[p + f"mlp.e{e}.down"] = (D, ff)
+            out[p + "mlp.router"] = (int(mlp["router"]["experts"]), D)
+    return out
+
+
+def random_weights(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Seeded bf16 weights with the design's tensor names: linear weights N(0, 1 / in), norm weights around 1,
+    router rows large enough to spread the choice and the scores over (0, 1)."""
+    g = torch.Generator().manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in tensor_shapes(cfg).items():
+        x = torch.randn(tuple(shape), generator=g)
+        if name.endswith("norm") or name.endswith("norm1"):
+            x = 1.0 + 0.2 * x
+        elif name.endswith("mlp.router"):
+            x = 2.0 * x / math.sqrt(shape[-1])
+        elif name != "embed":
+            x = x / math.sqrt(shape[-1])
+        out[name] = x.to(torch.bfloat16)
+    return out
