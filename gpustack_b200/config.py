@@ -244,7 +244,7 @@ class AttentionSpec:
     def tile_sized(self) -> bool:
         """Keys and values share one width that is a tensor-core tile (64 / 128) and the group fits the decode
         kernel: the Llama-class attention kernels (with sink and gate) can serve this mixer in bf16."""
-        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16 and not self.window
+        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
 
     @property
     def out_width(self) -> int:

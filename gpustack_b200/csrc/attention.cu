@@ -80,7 +80,8 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
                          const int32_t* __restrict__ seq_lens, bf16* __restrict__ out,
                          float* __restrict__ ws_o, float* __restrict__ ws_ml, int num_splits,
                          int Hq, int Hkv, float scale_log2, uint32_t* __restrict__ split_ctr,
-                         const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride) {
+                         const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride,
+                         int window) {
   pdl_launch_dependents();
   pdl_wait();
   using Cfg = DecCfg<D>;
@@ -92,8 +93,12 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq_len = seq_lens[b];
   const int n_pages = (seq_len + kPage - 1) / kPage;
-  const int pps = (n_pages + num_splits - 1) / num_splits;
-  const int p_begin = split * pps;
+  // a sliding window (> 0): the row at position seq_len - 1 sees keys [seq_len - window, seq_len); the splits share
+  // the pages from the one that holds the window's first key
+  const int first_key = window > 0 ? max(0, seq_len - window) : 0;
+  const int p_first = first_key / kPage;
+  const int pps = (n_pages - p_first + num_splits - 1) / num_splits;
+  const int p_begin = p_first + split * pps;
   const int p_end = min(n_pages, p_begin + pps);
 
   // ---- stage Q (G rows, zero-padded to 16) in swizzled smem
@@ -174,7 +179,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int tok = tok0 + t * 8 + (e & 1);
-        const float v = tok < seq_len ? s[t][e] * scale_log2 : -INFINITY;
+        const float v = (tok < seq_len && tok >= first_key) ? s[t][e] * scale_log2 : -INFINITY;
         s[t][e] = v;
         if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
@@ -725,6 +730,17 @@ extern "C" int b200_paged_attn_decode_ex(const void* q, int64_t q_stride, const 
                                          void* workspace, int num_splits, int B, int Hq, int Hkv,
                                          int D, int block_size, float scale, const float* sink,
                                          const void* gate, int64_t gate_stride, void* stream) {
+  return b200_paged_attn_decode_win(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_lens, out, workspace,
+                                    num_splits, B, Hq, Hkv, D, block_size, scale, sink, gate, gate_stride, 0, stream);
+}
+
+extern "C" int b200_paged_attn_decode_win(const void* q, int64_t q_stride, const void* k_cache,
+                                          const void* v_cache, const int32_t* block_table,
+                                          int max_blocks, const int32_t* seq_lens, void* out,
+                                          void* workspace, int num_splits, int B, int Hq, int Hkv,
+                                          int D, int block_size, float scale, const float* sink,
+                                          const void* gate, int64_t gate_stride, int window, void* stream) {
+  B200_REQUIRE(window >= 0, "attn_decode: window %d", window);
   B200_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attn_decode: bad head counts");
   B200_REQUIRE(Hq / Hkv <= 16, "attn_decode: group size %d > 16 unsupported", Hq / Hkv);
   B200_REQUIRE(block_size == kPage, "attn_decode: block_size must be %d", kPage);
@@ -752,7 +768,7 @@ extern "C" int b200_paged_attn_decode_ex(const void* q, int64_t q_stride, const 
     (void)launch_pdl(paged_attn_decode_kernel<128>, dim3(grid), dim3(kDecWarps * 32), DecCfg<128>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride);
+        (const bf16*)gate, gate_stride, window);
     rc = b200_check_launch("b200_paged_attn_decode");
   } else {
     static bool once = false;
@@ -764,7 +780,7 @@ extern "C" int b200_paged_attn_decode_ex(const void* q, int64_t q_stride, const 
     (void)launch_pdl(paged_attn_decode_kernel<64>, dim3(grid), dim3(kDecWarps * 32), DecCfg<64>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride);
+        (const bf16*)gate, gate_stride, window);
     rc = b200_check_launch("b200_paged_attn_decode");
   }
   return rc;
@@ -784,7 +800,8 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
                           int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
                           void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream,
-                          const float* sink = nullptr, const void* gate = nullptr, int64_t gate_stride = 0);
+                          const float* sink = nullptr, const void* gate = nullptr, int64_t gate_stride = 0,
+                          int window = 0);
 }  // namespace b200
 
 extern "C" int b200_attn_prefill_tc_covers(int Hq, int Hkv, int D) {
@@ -799,12 +816,24 @@ extern "C" int b200_paged_attn_prefill_ex(const void* q, int64_t q_stride, int n
                                           const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
                                           int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
                                           const void* gate, int64_t gate_stride, void* stream) {
+  return b200_paged_attn_prefill_win(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,
+                                     ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, block_size, scale, sink, gate,
+                                     gate_stride, 0, stream);
+}
+
+extern "C" int b200_paged_attn_prefill_win(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
+                                           const void* v_cache, int num_blocks, const int32_t* block_table,
+                                           int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                           const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
+                                           int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                           const void* gate, int64_t gate_stride, int window, void* stream) {
+  B200_REQUIRE(window >= 0, "attn_prefill_ex: window %d", window);
   B200_REQUIRE(b200_attn_prefill_tc_covers(Hq, Hkv, D), "attn_prefill_ex: heads %d / %d x %d not covered", Hq, Hkv, D);
   B200_REQUIRE(block_size == kPage, "attn_prefill_ex: block_size must be %d", kPage);
   if (num_tiles <= 0) return B200_OK;
   const int rc = paged_attn_prefill_tc(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks,
                                        cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, scale,
-                                       (cudaStream_t)stream, sink, gate, gate_stride);
+                                       (cudaStream_t)stream, sink, gate, gate_stride, window);
   if (rc > 0) {
     b200_set_error("attn_prefill_ex: the tensor-core kernel does not take this call (alignment or device)");
     return B200_ERR_UNSUPPORTED;

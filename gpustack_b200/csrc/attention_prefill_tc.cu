@@ -75,7 +75,8 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                              const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
                              const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                              int num_tiles, bf16* __restrict__ out, int Hq, int Hkv, float scale_log2,
-                             const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride) {
+                             const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride,
+                             int window) {
   constexpr int TPT = 128 / G;   // query tokens per tile
   extern __shared__ uint8_t fa_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) &
@@ -130,6 +131,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // one work item = (tile, kv-head); tiles are listed heaviest first, the kv-heads of a tile are adjacent
   struct Work {
     int seq, kvh, q0, q_begin, q_len, ctx, total_len, n_blocks, n_pages_seq;
+    int j0;   // first KV block the tile reads: 0, or with a sliding window the block of its first row's first key
   };
   const int total_work = num_tiles * Hkv;
   auto load_work = [&](int w) {
@@ -145,6 +147,10 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     m.total_len = m.ctx + m.q_len;
     const int kv_end = min(m.total_len, m.ctx + m.q0 + TPT);   // causal horizon of the tile (exclusive)
     m.n_blocks = (kv_end + kFaKv - 1) / kFaKv;                 // >= 1
+    // sliding window (> 0): position i sees j with 0 <= i - j < window.  The tile's first row starts at
+    // lo = ctx + q0 - window + 1 < kv_end, so j0 < n_blocks; all three roles walk blocks [j0, n_blocks)
+    const int lo = window > 0 ? m.ctx + m.q0 - window + 1 : 0;
+    m.j0 = lo > 0 ? lo / kFaKv : 0;
     m.n_pages_seq = (m.total_len + kFaPage - 1) / kFaPage;
     return m;
   };
@@ -182,9 +188,9 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       const int32_t* bt = block_table + (size_t)m.seq * max_blocks;
       int my_blk = 0;
-      for (int j = 0; j < m.n_blocks; ++j) {
-        if ((j & 7) == 0) {   // refill: pages [j*4, j*4 + 32)
-          const int page = j * PPB + lane;
+      for (int j = m.j0; j < m.n_blocks; ++j) {
+        if ((j & 7) == 0 || j == m.j0) {   // refill: the 32 pages of the 8 blocks around j
+          const int page = (j & ~7) * PPB + lane;
           my_blk = page < m.n_pages_seq ? __ldg(bt + page) : 0;   // block 0: the all-zero null block
         }
         int rows[PPB];
@@ -239,7 +245,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       uint32_t gb = 0, it = 0;
       Work nxt = load_work(work_of(0));
       for (int rd = 0; rd < n_rounds; ++rd) {
-        const int n_blocks = nxt.n_blocks;
+        const int n_blocks = nxt.n_blocks - nxt.j0;   // blocks the tile reads (>= 1); j counts them from 0 here
         nxt = load_work(work_of(rd + 1));
         if (work_of(rd) >= total_work) break;
         mbar_wait_guarded(q_full, it & 1);
@@ -298,7 +304,8 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const int total_len = m.total_len;
       float m_used = -INFINITY, l = 0.f;
 
-      for (int j = 0; j < m.n_blocks; ++j, ++gb) {
+      const int row_lo = window > 0 ? qpos - window + 1 : 0;   // first key this row sees
+      for (int j = m.j0; j < m.n_blocks; ++j, ++gb) {
         const uint32_t s_col = (gb & 1) * kFaKv;
         mbar_wait_guarded(&s_full[gb & 1], (gb >> 1) & 1);
         tc_fence_after();
@@ -308,13 +315,14 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tmem_ld_wait();
         const int kv0 = j * kFaKv;
         // block-uniform: does any row of the tile see a masked column in this block?
-        const bool need_mask = (kv0 + kFaKv - 1 > m.ctx + m.q0) || (kv0 + kFaKv - 1 >= total_len);
+        const bool need_mask = (kv0 + kFaKv - 1 > m.ctx + m.q0) || (kv0 + kFaKv - 1 >= total_len) ||
+                               (window > 0 && kv0 < m.ctx + m.q0 + TPT - window);
         if (need_mask) {   // ONE warp-uniform branch per block (the condition is tile-uniform), not one per column
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int ka = kv0 + c, kb = kv0 + 32 + c;
-            if (ka > qpos || ka >= total_len) s0[c] = 0xff800000u;   // -inf
-            if (kb > qpos || kb >= total_len) s1[c] = 0xff800000u;
+            if (ka > qpos || ka >= total_len || ka < row_lo) s0[c] = 0xff800000u;   // -inf
+            if (kb > qpos || kb >= total_len || kb < row_lo) s1[c] = 0xff800000u;
           }
         }
         // row maximum on the raw scores (scale > 0 commutes with max); the scale itself is folded
@@ -331,11 +339,12 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           alpha = ex2_approx(m_used - mx);
           m_used = mx;
           l *= alpha;
-          rescale = j > 0;
+          rescale = j > m.j0;
         }
         uint32_t pk[32];
         float sum = 0.f;
-        const float neg_m = -m_used;
+        // a row whose window starts after this block has seen nothing yet (m_used = -inf): its probabilities are 0
+        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           const float p0 = ex2_approx(fmaf(__uint_as_float(s0[c]), scale_log2, neg_m));
@@ -350,7 +359,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const bool any_rescale = __any_sync(0xffffffffu, rescale);
         // the previous block's PV (possibly the previous tile's last) must have retired before the
         // shared-memory P buffer is overwritten / before O is rescaled (any_rescale implies j > 0)
-        if ((j > 0 || it > 0) && (!P_TMEM || any_rescale)) {
+        if ((j > m.j0 || it > 0) && (!P_TMEM || any_rescale)) {
           mbar_wait_guarded(p_empty, (gb - 1) & 1);
           tc_fence_after();
         }
@@ -468,7 +477,7 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
                              const void* v_cache, int num_blocks, const int32_t* block_table, int max_blocks,
                              const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                              const int32_t* tile_q0, int num_tiles, void* out, int Hq, int Hkv, float scale,
-                             const float* sink, const void* gate, int64_t gate_stride, cudaStream_t stream) {
+                             const float* sink, const void* gate, int64_t gate_stride, int window, cudaStream_t stream) {
   auto kernel = paged_attn_prefill_tc_kernel<G, P_TMEM>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -500,7 +509,7 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
   const int grid = (int)(persist ? (total_work < 2LL * sms ? total_work : 2LL * sms) : total_work);
   cudaError_t e = launch_pdl(kernel, dim3(grid), dim3(kFaThreads), (size_t)kFaSmemBytes, stream, 1, tq, tk, tv,
                              block_table, max_blocks, cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, (bf16*)out, Hq,
-                             Hkv, scale_log2, sink, (const bf16*)gate, gate_stride);
+                             Hkv, scale_log2, sink, (const bf16*)gate, gate_stride, window);
   if (e != cudaSuccess) {
     b200_set_error("b200_paged_attn_prefill(tc): launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
@@ -515,7 +524,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
                           int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
                           void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream, const float* sink,
-                          const void* gate, int64_t gate_stride) {
+                          const void* gate, int64_t gate_stride, int window) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("B200_ATTN_PREFILL_TC");   // =0: keep the mma.sync kernels (A/B runs)
@@ -533,7 +542,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
   }
 #define B200_FA_LAUNCH(GG, PT)                                                                                       \
   launch_prefill_tc<GG, PT>(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,    \
-                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, sink, gate, gate_stride, stream)
+                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, sink, gate, gate_stride, window, stream)
   if (G == 4) return p_tmem ? B200_FA_LAUNCH(4, true) : B200_FA_LAUNCH(4, false);
   return p_tmem ? B200_FA_LAUNCH(8, true) : B200_FA_LAUNCH(8, false);
 #undef B200_FA_LAUNCH

@@ -247,13 +247,14 @@ class LayerListRunner(ModelRunner):
     def _decode_plan(self, B: int, m):
         """(KV splits, workspace) of the split-KV decode kernel for B rows of mixer m; one zero-initialised,
         self-resetting workspace per head shape, sized for the largest batch."""
-        splits = ops.attn_decode_splits(B, m.kv_heads, self.max_model_len)
-        key = (m.heads, m.kv_heads, m.dim)
+        span = min(self.max_model_len, m.window) if m.window else self.max_model_len    # keys a row can see
+        splits = ops.attn_decode_splits(B, m.kv_heads, span)
+        key = (m.heads, m.kv_heads, m.dim, span)
         if key not in self._dec_ws:
             from .lib import load
 
             L = load()
-            need = max(L.b200_attn_decode_workspace_bytes(b, m.heads, m.dim, ops.attn_decode_splits(b, m.kv_heads, self.max_model_len))
+            need = max(L.b200_attn_decode_workspace_bytes(b, m.heads, m.dim, ops.attn_decode_splits(b, m.kv_heads, span))
                        for b in range(1, self.max_seqs + 1))
             self._dec_ws[key] = torch.zeros((need + 3) // 4, dtype=torch.float32, device=self.device)
         return splits, self._dec_ws[key]
@@ -303,7 +304,8 @@ class LayerListRunner(ModelRunner):
                 kc, vc = self.k_cache[l], self.v_cache[l]
                 if nt and self.fast_prefill[li]:
                     ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, out[:Tp], H, G, dk,
-                                              m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None)
+                                              m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None,
+                                              window=m.window)
                 elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
                                           H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window)
@@ -311,7 +313,7 @@ class LayerListRunner(ModelRunner):
                     splits, ws = self._decode_plan(Bd, m)
                     ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
                                           num_splits=splits, workspace=ws, sink=lw.sink,
-                                          gate=proj[Tp:T, gate_col:] if m.gate else None)
+                                          gate=proj[Tp:T, gate_col:] if m.gate else None, window=m.window)
                 elif Bd:
                     ops.attn_sink_decode(proj[Tp:T], gate_col, kc, vc, bt_d, lens_d, lw.sink, out[Tp:T], H, G, dk, dv,
                                          m.scale, window=m.window)

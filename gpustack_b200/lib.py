@@ -87,6 +87,10 @@ SIGNATURES = {
                                           _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _vp]),
     "b200_paged_attn_decode_ex": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
                                          _i32, _i32, _i32, _f32, _vp, _vp, _i64, _vp]),
+    "b200_paged_attn_prefill_win": (_i32, [_vp, _i64, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp,
+                                           _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _vp]),
+    "b200_paged_attn_decode_win": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
+                                          _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _vp]),
     "b200_gemm_bf16_relu2": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp]),
     "b200_mlstm_state_slices": (_i32, [_i32]),
     "b200_mlstm_scan": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,

@@ -367,15 +367,16 @@ def attn_decode_workspace(B, Hq, D, num_splits, device) -> torch.Tensor:
 
 
 def paged_attn_decode(q, q_stride, k_cache, v_cache, block_table, seq_lens, out, Hq, Hkv, D, scale,
-                      num_splits=1, workspace=None, sink=None, gate=None):
+                      num_splits=1, workspace=None, sink=None, gate=None, window: int = 0):
     """q: [B, >=Hq*D] view into the qkv buffer (row stride q_stride elements).  sink [Hq] fp32: softmax sink;
-    gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate)."""
+    gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate); window > 0: the
+    row at position n - 1 sees keys [n - window, n)."""
     B = seq_lens.shape[0]
     _req(block_table, torch.int32, "block_table"); _req(seq_lens, torch.int32, "seq_lens")
-    check(load().b200_paged_attn_decode_ex(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
-                                           block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
-                                           num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
-                                           0 if gate is None else gate.stride(0), _stream()),
+    check(load().b200_paged_attn_decode_win(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
+                                            block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
+                                            num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
+                                            0 if gate is None else gate.stride(0), int(window), _stream()),
           "paged_attn_decode")
     return out
 
@@ -405,14 +406,15 @@ def attn_prefill_tc_covers(Hq, Hkv, D) -> bool:
 
 
 def paged_attn_prefill_ex(q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, out, Hq, Hkv, D,
-                          scale, sink=None, gate=None):
-    """The tcgen05 prefill kernel with a softmax sink ([Hq] fp32) and / or a sigmoid output gate (bf16 view
-    [T, >=Hq*D]); only for shapes attn_prefill_tc_covers() accepts, tiles of attn_prefill_tile(Hq, Hkv) rows."""
-    check(load().b200_paged_attn_prefill_ex(_p(q), q_stride, q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0],
-                                            _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
-                                            _p(tile_q0), tile_seq.shape[0], _p(out), Hq, Hkv, D, k_cache.shape[2], scale,
-                                            _p(sink), _p(gate), 0 if gate is None else gate.stride(0), _stream()),
-          "paged_attn_prefill_ex")
+                          scale, sink=None, gate=None, window: int = 0):
+    """The tcgen05 prefill kernel with a softmax sink ([Hq] fp32), a sigmoid output gate (bf16 view [T, >=Hq*D])
+    and / or a sliding window (position i sees j with 0 <= i - j < window); only for shapes
+    attn_prefill_tc_covers() accepts, tiles of attn_prefill_tile(Hq, Hkv) rows."""
+    check(load().b200_paged_attn_prefill_win(_p(q), q_stride, q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0],
+                                             _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
+                                             _p(tile_q0), tile_seq.shape[0], _p(out), Hq, Hkv, D, k_cache.shape[2], scale,
+                                             _p(sink), _p(gate), 0 if gate is None else gate.stride(0), int(window),
+                                             _stream()), "paged_attn_prefill_ex")
     return out
 
 

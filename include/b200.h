@@ -409,6 +409,16 @@ int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col
                              const int32_t* block_table, int max_blocks, const int32_t* seq_lens, int B, const float* sink,
                              void* out, int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
                              int window, void* stream);
+/* The tensor-core attention kernels (tcgen05 prefill, split-KV decode) with a sliding window (0 = none). */
+int b200_paged_attn_prefill_win(const void* q, int64_t q_stride, int num_tokens, const void* k_cache, const void* v_cache,
+                                int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                                const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
+                                void* out, int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                const void* gate, int64_t gate_stride, int window, void* stream);
+int b200_paged_attn_decode_win(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                               const int32_t* block_table, int max_blocks, const int32_t* seq_lens, void* out,
+                               void* workspace, int num_splits, int B, int Hq, int Hkv, int D, int block_size, float scale,
+                               const float* sink, const void* gate, int64_t gate_stride, int window, void* stream);
 /* b200_moe_route_biased with sigmoid scores (sigmoid_scores != 0) and / or weights that are not renormalised. */
 int b200_moe_route_scored(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids, float* topk_w, int T,
                           int E, int K, float scale, int sigmoid_scores, int renormalize, void* stream);

@@ -40,7 +40,7 @@ def test_config_reader_round_trip_runs_and_rejections(tmp_path):
     assert abs(ret.k_scale - 12 ** -0.5) < 1e-12 and ret.decay == (0.97, 0.8)
     assert (att.window, att.values_are_keys, att.qk_unit_norm, att.rot.layout, att.sink, att.gate, att.qkv_bias) == \
         (7, True, True, "interleaved", False, False, False)
-    assert not att.tile_sized
+    assert not att.tile_sized                                            # 10-wide heads: the generic kernels
     e = c.layers[0].mlp.moe
     assert (e.experts, e.top, e.ff, e.score, e.renormalize, e.weight_on, e.act, e.identity) == (5, 2, 18, "sigmoid", False, "input", "silu", 0)
     # four attention runs (layer 1 three times, layer 3 once) hold keys and values; three runs of each recurrent layer hold state

@@ -372,6 +372,53 @@ def test_a_key_just_inside_the_window_dominates_and_just_outside_is_unseen(dtype
         assert _rel(od, want[i:]) < KTOL[dtype]
 
 
+def _run_window_tc(q, kc, vc, perm, H, G, dk, window, scale, start, n, splits):
+    """The tensor-core routes (tcgen05 prefill tiles, split-KV decode) over the same cache."""
+    from gpustack_b200 import ops
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")   # noqa: E731
+    rows = q[start:n].reshape(n - start, H * dk).cuda().contiguous()
+    out = torch.zeros_like(rows)
+    ts, tq = ops.build_prefill_tiles([n - start], ops.attn_prefill_tile(H, G), [start])
+    bt = perm.cuda().reshape(1, -1)
+    ops.paged_attn_prefill_ex(rows, rows.stride(0), kc, vc, bt, i32([0, n - start]), i32([start]), i32(ts), i32(tq), out, H, G,
+                              dk, scale, window=window)
+    last = q[n - 1:n].reshape(1, H * dk).cuda().contiguous()
+    od = torch.zeros_like(last)
+    ws = ops.attn_decode_workspace(1, H, dk, splits, "cuda")
+    ops.paged_attn_decode(last, last.stride(0), kc, vc, bt, i32([n]), od, H, G, dk, scale, num_splits=splits, workspace=ws,
+                          window=window)
+    return out.cpu(), od.cpu()
+
+
+@pytest.mark.parametrize("window,n,start,splits", [(40, 300, 0, 1), (64, 300, 33, 3), (65, 257, 64, 2), (200, 300, 100, 4),
+                                                   (1, 130, 7, 1), (1000, 300, 0, 2), (129, 400, 250, 8)])
+def test_sliding_window_on_the_tensor_core_attention_kernels(window, n, start, splits):
+    """128-wide heads in groups of four, bf16: the tcgen05 prefill kernel skips the key blocks before a tile's window
+    and masks inside the first one; the split-KV decode kernel divides only the window's pages among its splits."""
+    H, G, dk, scale = 8, 2, 128, 0.09
+    q, k, v, kc, vc, perm = _window_case(BF, n, H, G, dk, window, seed=17)
+    want = O.window_softmax_attention(q.to(F64), k.to(F64), v.to(F64), scale, window).reshape(n, -1)
+    out, od = _run_window_tc(q, kc, vc, perm, H, G, dk, window, scale, start, n, splits)
+    assert _rel(out, want[start:]) < KTOL[BF]
+    assert _rel(od, want[n - 1:]) < KTOL[BF]
+
+
+@pytest.mark.parametrize("window,i", [(64, 127), (65, 128), (33, 200), (128, 191), (40, 100), (1, 70)])
+@pytest.mark.parametrize("inside", [True, False])
+def test_window_edges_on_the_tensor_core_attention_kernels(window, i, inside):
+    H, G, dk, scale = 8, 2, 128, 0.25
+    j = i - window + 1 if inside else i - window
+    n = i + 1
+    q, k, v, kc, vc, perm = _window_case(BF, n, H, G, dk, window, seed=19, stand=(i, j))
+    want = O.window_softmax_attention(q.to(F64), k.to(F64), v.to(F64), scale, window).reshape(n, -1)
+    assert (float(want[i, :dk].min()) > 9.9) == inside
+    for start in sorted({0, max(0, j - 3), j, i}):
+        out, od = _run_window_tc(q, kc, vc, perm, H, G, dk, window, scale, start, n, 2)
+        assert _rel(out, want[start:]) < KTOL[BF], start
+        assert _rel(od, want[i:]) < KTOL[BF]
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
 @pytest.mark.parametrize("D,E,top,ff", [(52, 5, 2, 18), (40, 1, 1, 16), (24, 3, 3, 30), (256, 4, 2, 128), (256, 70, 4, 128)])
 def test_sigmoid_routed_experts_weighted_on_their_input(dtype, D, E, top, ff):
