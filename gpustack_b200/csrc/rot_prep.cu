@@ -138,6 +138,139 @@ rot_prep_kernel(RotPrepArgs a) {
   }
 }
 
+// The same steps with 16-byte accesses, one CTA per token: the token's cos / sin are computed ONCE (dims / 2 angles)
+// into shared memory and used by every head.  A head is cut into items of VEC = 16 bytes / sizeof(TA) entries: an
+// interleaved rotation turns the pairs inside an item; a half-split rotation makes an item of the piece [d, d + VEC)
+// and its partner [d + dims/2, ...); the unrotated rest are plain items.  LPH lanes (a power of two >= items per
+// head) share a head, a warp covers 32 / LPH head slots at a time, the sum of squares is reduced inside the group.
+constexpr int kRvThreads = 256;
+
+template <typename TA, typename TD>
+__global__ void __launch_bounds__(kRvThreads)
+rot_prep_vec_kernel(RotPrepArgs a, int lph, int items_q, int items_v) {
+  constexpr int VEC = 16 / (int)sizeof(TA);
+  extern __shared__ float2 cs[];                      // [dims / 2] (cos, sin) of this token
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, dims = a.dims, half = dims >> 1;
+  if (dims > 0) {
+    const int pos = a.positions[t];
+    for (int j = threadIdx.x; j < half; j += kRvThreads) {
+      const double ang = (double)pos * a.freq[j];
+      const float rem = (float)(ang - 6.283185307179586 * rint(ang * 0.15915494309189535));
+      float sn, c;
+      sincosf(rem, &sn, &c);
+      cs[j] = make_float2(c, sn);
+    }
+    __syncthreads();
+  }
+  const bool has_v = a.v_col >= 0;
+  const int n_slots = H + G + (has_v ? G : 0);
+  const int per_warp = 32 / lph, sub = lane / lph, li = lane % lph;
+  const int slot = a.paged ? a.slots[t] : 0;
+  const TA* row = reinterpret_cast<const TA*>(a.proj) + (size_t)t * a.ld;
+  const int n_rot = dims == 0 ? 0 : (a.half_layout ? half / VEC : dims / VEC);
+  for (int hs0 = warp * per_warp; hs0 < n_slots; hs0 += (kRvThreads / 32) * per_warp) {
+    const int hs = hs0 + sub;
+    const bool live = hs < n_slots;
+    const bool is_q = live && hs < H, is_k = live && !is_q && hs < H + G, is_v = live && !is_q && !is_k;
+    const int g = is_q ? hs : (is_k ? hs - H : hs - H - G);
+    const bool act = live && li < (is_v ? items_v : items_q) && (is_q || !a.paged || slot >= 0);
+    float x0[VEC], x1[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) x0[i] = x1[i] = 0.f;
+    int d0 = 0, d1 = -1;
+    float ss = 0.f;
+    TD* dst = nullptr;
+    if (act) {
+      const size_t cache_row = a.paged ? ((size_t)(slot / a.page) * G + g) * a.page + (slot % a.page) : 0;
+      const TA* src = row + (is_q ? a.q_col + g * dk : (is_k ? a.k_col + g * dk : a.v_col + g * dv));
+      if (is_q) dst = reinterpret_cast<TD*>(a.q_out) + (size_t)t * a.ldq + g * dk;
+      else if (is_k) dst = reinterpret_cast<TD*>(a.k_out) + (a.paged ? cache_row * dk : (size_t)t * a.ldk + g * dk);
+      else dst = reinterpret_cast<TD*>(a.v_out) + (a.paged ? cache_row * dv : (size_t)t * a.ldv + g * dv);
+      const bool rot = !is_v && li < n_rot;
+      d0 = is_v ? li * VEC : (rot ? li * VEC : dims + (li - n_rot) * VEC);
+      if (rot && a.half_layout) d1 = d0 + half;
+      {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + d0);
+        const TA* rv = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x0[i] = rp_f32(rv[i]);
+      }
+      if (d1 >= 0) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + d1);
+        const TA* rv = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x1[i] = rp_f32(rv[i]);
+      }
+      if (is_k && !has_v && a.v_out != nullptr) {      // the values are the keys as projected
+        TD* vdst = reinterpret_cast<TD*>(a.v_out) + (a.paged ? cache_row * dv : (size_t)t * a.ldv + g * dv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) rp_store(vdst + d0 + i, x0[i]);
+        if (d1 >= 0) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) rp_store(vdst + d1 + i, x1[i]);
+        }
+      }
+      if (a.feature == 1) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          x0[i] = x0[i] / (1.0f + expf(-x0[i]));
+          if (d1 >= 0) x1[i] = x1[i] / (1.0f + expf(-x1[i]));
+        }
+      }
+      if (rot && a.half_layout) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const float2 c = cs[d0 + i];
+          const float u = x0[i], v = x1[i];
+          x0[i] = u * c.x - v * c.y;
+          x1[i] = v * c.x + u * c.y;
+        }
+      } else if (rot) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 2) {
+          const float2 c = cs[(d0 + i) >> 1];
+          const float u = x0[i], v = x0[i + 1];
+          x0[i] = u * c.x - v * c.y;
+          x0[i + 1] = v * c.x + u * c.y;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        ss = fmaf(x0[i], x0[i], ss);
+        if (d1 >= 0) ss = fmaf(x1[i], x1[i], ss);
+      }
+    }
+    float mul = is_q ? a.q_mul : a.k_mul;
+    if (a.unit_norm) {                                 // every lane takes part in the shuffles
+      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      mul *= 1.0f / sqrtf(ss / (float)dk + a.eps);
+    }
+    if (!act) continue;
+    if (is_v) mul = 1.0f;
+    // 16-byte stores whatever the destination type: VEC fp32 entries are VEC / 4 pieces, VEC bf16 entries one
+    if constexpr (sizeof(TD) == 4) {
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + d0 + i) =
+            make_float4(x0[i] * mul, x0[i + 1] * mul, x0[i + 2] * mul, x0[i + 3] * mul);
+        if (d1 >= 0)
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + d1 + i) =
+              make_float4(x1[i] * mul, x1[i + 1] * mul, x1[i + 2] * mul, x1[i + 3] * mul);
+      }
+    } else {
+      uint32_t w0[VEC / 2], w1[VEC / 2];
+#pragma unroll
+      for (int i = 0; i < VEC; i += 2) {
+        w0[i / 2] = pack_bf16(x0[i] * mul, x0[i + 1] * mul);
+        w1[i / 2] = pack_bf16(x1[i] * mul, x1[i + 1] * mul);
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + d0) = *reinterpret_cast<uint4*>(w0);
+      if (d1 >= 0) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + d1) = *reinterpret_cast<uint4*>(w1);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -161,6 +294,29 @@ extern "C" int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_co
   const int n_slots = H + G + (v_col >= 0 ? G : 0);
   dim3 grid(T, (n_slots + kRpWarps - 1) / kRpWarps);
   cudaStream_t s = (cudaStream_t)stream;
+  {
+    // 16-byte path: every width, column offset, leading dimension and base address a multiple of 16 bytes on both
+    // sides, rotated part a whole number of items, at most 32 items per head
+    const int esz = src_f32 ? 4 : 2, dsz = dst_f32 ? 4 : 2, vec = 16 / esz;
+    auto al = [](const void* p_) { return (reinterpret_cast<uintptr_t>(p_) & 15) == 0; };
+    const bool has_v = v_col >= 0;
+    const int rot_items = dims == 0 ? 0 : (half_layout ? (dims / 2) / vec : dims / vec);
+    const int items_q = rot_items + (dk - dims) / vec, items_v = dv / vec;
+    const int items = items_q > items_v ? items_q : items_v;
+    bool ok = dk % vec == 0 && dv % vec == 0 && dims % vec == 0 && (!half_layout || (dims / 2) % vec == 0) && items <= 32 &&
+              ld % vec == 0 && q_col % vec == 0 && k_col % vec == 0 && (!has_v || v_col % vec == 0) && al(proj) && al(q_out) &&
+              al(k_out) && al(v_out) && (ldq * dsz) % 16 == 0 && (paged || ((ldk * dsz) % 16 == 0 && (ldv * dsz) % 16 == 0)) &&
+              (size_t)(dims / 2) * sizeof(float2) <= 40 * 1024 && !(src_f32 && !dst_f32);
+    if (ok) {
+      int lph = 1;
+      while (lph < items) lph <<= 1;
+      const size_t smem = (size_t)(dims / 2) * sizeof(float2);
+      if (src_f32) rot_prep_vec_kernel<float, float><<<T, kRvThreads, smem, s>>>(a, lph, items_q, items_v);
+      else if (dst_f32) rot_prep_vec_kernel<bf16, float><<<T, kRvThreads, smem, s>>>(a, lph, items_q, items_v);
+      else rot_prep_vec_kernel<bf16, bf16><<<T, kRvThreads, smem, s>>>(a, lph, items_q, items_v);
+      return b200_check_launch("b200_rot_prep");
+    }
+  }
   if (src_f32) rot_prep_kernel<float, float><<<grid, kRpWarps * 32, 0, s>>>(a);
   else if (dst_f32) rot_prep_kernel<bf16, float><<<grid, kRpWarps * 32, 0, s>>>(a);
   else rot_prep_kernel<bf16, bf16><<<grid, kRpWarps * 32, 0, s>>>(a);

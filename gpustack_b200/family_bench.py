@@ -1,6 +1,7 @@
-"""Side benchmark of the layer-list family (Vodavik, Danipel) beside the closest Llama-class model of equal layer sizes.
+"""Side benchmark of the layer-list family (Vodavik, Danipel, Resevik) beside the closest existing model of equal layer
+sizes (a Llama-class decoder; for Resevik also Vodavik, the other design with attention and recurrent-state layers).
 
-`python bench.py --family vodavik|danipel` prints ONE JSON line (not the serving benchmark's line; that workload and its
+`python bench.py --family vodavik|danipel|resevik` prints ONE JSON line (not the serving benchmark's line; that workload and its
 contract are untouched).  Random weights, synthetic tokens.  Two kinds of numbers:
 
   model:   prefill tokens/s (prompts of `prompt` tokens, `seqs` at a time through runner.prefill) and decode tokens/s
@@ -21,8 +22,8 @@ import numpy as np
 import torch
 
 from . import ops
-from .config import (AttentionSpec, EngineConfig, LatentAttentionSpec, LayerListConfig, LayerSpec, MLPSpec, MLSTMSpec, ModelConfig,
-                     MoESpec, RotarySpec)
+from .config import (AttentionSpec, EngineConfig, LatentAttentionSpec, LayerListConfig, LayerSpec, LinearAttentionSpec, MLPSpec,
+                     MLSTMSpec, ModelConfig, MoESpec, RotarySpec)
 
 ROOT = Path(__file__).resolve().parent.parent
 SIZES = {
@@ -61,6 +62,39 @@ def danipel_config(size: str, layers: int = 4) -> LayerListConfig:
         specs.append(LayerSpec(mix, mlp))
     return LayerListConfig("Danipel", V, D, specs, norm_eps=1e-6, residual="streams", norm="tanh", streams=2,
                            residual_mult=0.7, embed_scale=1.0)
+
+
+# Resevik at the same widths: half as many 128 x 128 linear-attention heads as attention heads (the recurrent layers of
+# the Vodavik benchmark have the same), a sliding window of half the prompt, 8 routed experts (2 chosen) of a quarter of
+# the dense feed-forward's width in every layer
+RESEVIK = {
+    # name: window, experts, top, expert ff
+    "2k": (1024, 8, 2, 2048),
+    "4k": (1024, 8, 2, 3584),
+}
+
+
+def resevik_config(size: str, layers: int = 4) -> LayerListConfig:
+    D, H, G, hd, ff, V = SIZES[size]
+    win, E, top, ffe = RESEVIK[size]
+    Hm = H // 2
+    decay = tuple(1.0 - 2.0 ** (-5 - 5 * i / max(1, Hm - 1)) for i in range(Hm))
+    specs = []
+    for i in range(layers):
+        if i % 2 == 1:
+            mix = AttentionSpec(H, G, hd, hd, hd ** -0.5, qk_norm=False, qkv_bias=False, sink=False, gate=False,
+                                rot=RotarySpec(dims=hd // 2, base=5e5, layout="interleaved"), qk_unit_norm=True, window=win,
+                                values_are_keys=True)
+        elif i % 4 == 0:
+            mix = LinearAttentionSpec(Hm, hd, hd, decay, feature=None, rot=RotarySpec(dims=hd, base=1e6, layout="half"),
+                                      k_scale=hd ** -0.5, out_norm="per_head", gate_act="silu", type_name="retention")
+        else:
+            mix = LinearAttentionSpec(Hm, hd, hd, decay, feature="silu", out_norm="all_heads", gate_act="sigmoid",
+                                      type_name="lightning")
+        mlp = MLPSpec("moe", ffe, act="silu", moe=MoESpec(experts=E, top=top, ff=ffe, limit=0.0, score="sigmoid",
+                                                          renormalize=False, weight_on="input", act="silu"))
+        specs.append(LayerSpec(mix, mlp))
+    return LayerListConfig("Resevik", V, D, specs, norm_eps=1e-5, residual="parallel", norm="rms", embed_scale=D ** 0.5)
 
 
 def _peaks():
@@ -437,7 +471,166 @@ def _kernel_numbers_danipel(size, T, B, ctx, log):
     return res
 
 
-FAMILIES = {"vodavik": (vodavik_config, _kernel_numbers), "danipel": (danipel_config, _kernel_numbers_danipel)}
+def _kernel_numbers_resevik(size, T, B, ctx, log):
+    """Resevik's kernels beside the like kernels of the closest models (Vodavik's norm, preparation, attention and
+    recurrence kernels; the Mixtral experts) at equal sizes."""
+    D, H, G, hd, ff, V = SIZES[size]
+    win, E, top, ffe = RESEVIK[size]
+    Hm = H // 2
+    hbm, flops_peak, how = _peaks()
+    flush = _Flush()
+    dev = "cuda"
+    bf, f32 = torch.bfloat16, torch.float32
+    rnd = lambda *s, dt=bf, sc=1.0: (torch.randn(*s, device=dev, dtype=f32) * sc).to(dt)   # noqa: E731
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)   # noqa: E731
+    res = {}
+
+    def put(name, new_s, new_work, like_name, like_s, like_work, kind):
+        peak = hbm if kind == "bytes" else flops_peak
+        fn, fl = new_work / new_s / peak, like_work / like_s / peak
+        res[name] = {"us": round(new_s * 1e6, 1), "frac_of_" + how + "_" + kind: round(fn, 3), "like": like_name,
+                     "like_us": round(like_s * 1e6, 1), "like_frac": round(fl, 3), "distance_ratio": round(fl / fn, 2)}
+        log(f"  {name:34s} {new_s * 1e6:9.1f} us  {fn:6.3f} of roofline | {like_name}: {like_s * 1e6:9.1f} us {fl:6.3f}"
+            f"  -> {fl / fn:5.2f}x as far")
+
+    # ---- residual sum of two branch outputs + RMS norm, vs the norm after the sum of the post-norm design
+    x32, ya, yb, w = rnd(T, D, dt=f32), rnd(T, D, dt=f32), rnd(T, D, dt=f32), rnd(D)
+    xb = torch.empty(T, D, device=dev, dtype=bf)
+    t_new = _time(lambda: ops.add_rms_norm(x32, w, 1e-5, a=ya, b=yb, x_out=x32, xb_out=xb), flush)
+    t_like = _time(lambda: ops.sum_layer_norm(ya, x32, w, 2.0, 1e-5, x_out=x32, xb_out=xb), flush)
+    put("add_rms_norm (2 branches)", t_new, T * D * 18.0, "sum_layer_norm", t_like, T * D * 14.0, "bytes")
+
+    # ---- rotation + unit norm + page scatter (values = keys), vs bias + head norms + temperature + page scatter
+    nblk = (B * ctx + T) // 16 + 8
+    proj = rnd(T, (H + G) * hd)
+    kc, vc = rnd(nblk, G, 16, hd), rnd(nblk, G, 16, hd)
+    pos, slots = i32(np.arange(T) % 4096), i32(np.arange(T))
+    freq = torch.tensor(RotarySpec(dims=hd // 2, base=5e5).frequencies()[0], dtype=torch.float64, device=dev)
+    t_new = _time(lambda: ops.rot_prep(proj, 0, H * hd, -1, pos, slots, proj, kc, vc, H, G, hd, hd, paged=True,
+                                       rot_dims=hd // 2, half_layout=False, freq=freq, unit_norm=True, eps=1e-5), flush)
+    Wv = (H + 2 * G) * hd + H * hd
+    projv = rnd(T, Wv)
+    bias, qn, kn = rnd((H + 2 * G) * hd), rnd(hd), rnd(hd)
+    t_prep = _time(lambda: ops.attn_prep(projv, bias, qn, kn, pos, slots, kc, vc, H, G, hd, hd, 1e-5, 0.1, 512), flush)
+    put("rot_prep (attention)", t_new, T * (2 * H + 3 * G) * hd * 2.0, "attn_prep", t_prep, T * (H + 2 * G) * hd * 4.0, "bytes")
+    # the recurrent mixers' preparation: bf16 rows in, fp32 q | k | v rows out
+    pl = rnd(T, 4 * Hm * hd, sc=0.5)
+    x32l = torch.empty(T, 3 * Hm * hd, device=dev)
+    freql = torch.tensor(RotarySpec(dims=hd, base=1e6).frequencies()[0], dtype=torch.float64, device=dev)
+    kcl, vcl = Hm * hd, 2 * Hm * hd
+    t_new = _time(lambda: ops.rot_prep(pl, 0, kcl, vcl, pos, None, x32l, x32l[:, kcl:], x32l[:, vcl:], Hm, Hm, hd, hd, paged=False,
+                                       rot_dims=hd, half_layout=True, freq=freql, k_mul=hd ** -0.5), flush)
+    put("rot_prep (retention, fp32 out)", t_new, T * 3 * Hm * hd * 6.0, "attn_prep", t_prep, T * (H + 2 * G) * hd * 4.0, "bytes")
+
+    # ---- prefill attention in a window: the tcgen05 kernel with and without the window
+    S = max(1, T // 2048)
+    L = T // S
+    tile = ops.attn_prefill_tile(H, G)
+    ts_, tq_ = ops.build_prefill_tiles([L] * S, tile, [0] * S)
+    nb = (L + 15) // 16
+    bt = i32(np.arange(S * nb).reshape(S, nb) + 1)
+    cu, ctx0 = i32(np.arange(S + 1) * L), i32(np.zeros(S))
+    out = torch.empty(T, H * hd, device=dev, dtype=bf)
+    ts_d, tq_d = i32(ts_), i32(tq_)
+    Wp = proj.shape[1]
+    t_new = _time(lambda: ops.paged_attn_prefill_ex(proj, Wp, kc, vc, bt, cu, ctx0, ts_d, tq_d, out, H, G, hd, hd ** -0.5,
+                                                    window=win), flush)
+    sink = rnd(H, dt=f32)
+    gate_col = (H + 2 * G) * hd
+    gate_v = projv[:, gate_col:]
+    t_like = _time(lambda: ops.paged_attn_prefill_ex(projv, Wv, kc, vc, bt, cu, ctx0, ts_d, tq_d, out, H, G, hd, hd ** -0.5,
+                                                     sink=sink, gate=gate_v), flush)
+    pairs_w = S * sum(min(i + 1, win) for i in range(L))
+    put("attention prefill, window tc", t_new, 4.0 * pairs_w * H * hd, "attention prefill, sink + gate tc", t_like,
+        4.0 * S * (L * L / 2) * H * hd, "flops")
+
+    # ---- decode attention in a window
+    nbd = (ctx + 16) // 16
+    btd = i32(np.arange(B * nbd).reshape(B, nbd) % (nblk - 1) + 1)
+    lens = i32(np.full(B, ctx))
+    outd = torch.empty(B, H * hd, device=dev, dtype=bf)
+    sp_w = ops.attn_decode_splits(B, G, min(ctx + 16, win))
+    ws_w = ops.attn_decode_workspace(B, H, hd, sp_w, dev)
+    pB = proj[:B]
+    t_new = _time(lambda: ops.paged_attn_decode(pB, Wp, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=sp_w,
+                                                workspace=ws_w, window=win), flush)
+    splits = ops.attn_decode_splits(B, G, ctx + 16)
+    ws = ops.attn_decode_workspace(B, H, hd, splits, dev)
+    pvB, gB = projv[:B], projv[:B, gate_col:]
+    t_like = _time(lambda: ops.paged_attn_decode(pvB, Wv, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=splits,
+                                                 workspace=ws, sink=sink, gate=gB), flush)
+    put("attention decode, window", t_new, B * min(ctx, win) * G * hd * 4.0, "attention decode, sink + gate", t_like,
+        B * ctx * G * hd * 4.0, "bytes")
+
+    # ---- decayed linear attention vs the matrix-memory recurrence: prompt portions and single rows
+    x32l.normal_(0.0, 0.3)
+    decay = torch.tensor([1.0 - 2.0 ** (-5 - 5 * i / max(1, Hm - 1)) for i in range(Hm)], device=dev)
+    nslot = max(S, B)
+    Sst = torch.zeros(nslot, Hm, hd, hd, device=dev)
+    o_raw = torch.empty(T, Hm * hd, device=dev)
+    slot_s, slot_b = i32(np.arange(S)), i32(np.arange(B))
+    t_new = _time(lambda: ops.linattn_scan(x32l, 0, kcl, vcl, decay, cu, ctx0, slot_s, Sst, o_raw, Hm, hd, hd, max_len=L), flush,
+                  iters=3, warm=1)
+    pm = rnd(T, 4 * Hm * hd, sc=0.5)
+    gates, gb = rnd(T, 2 * Hm, dt=f32), rnd(2 * Hm)
+    Z = ops.mlstm_state_slices(hd)
+    nst, mst = torch.zeros(nslot, Hm, Z, hd, device=dev), torch.zeros(nslot, Hm, Z, device=dev)
+    Sm = torch.zeros(nslot, Hm, hd, hd, device=dev)
+    t_like = _time(lambda: ops.mlstm_scan(pm, 0, Hm * hd, 2 * Hm * hd, gates, gb, cu, ctx0, slot_s, Sm, nst, mst, o_raw, Hm, hd, hd,
+                                          15.0, max_len=L), flush, iters=3, warm=1)
+    fma_peak = 148 * 128 * 2 * 1.9e9          # fp32 FMA rate: the recurrence's products are fp32 by the exactness rule
+    wl = 6.0 * T * Hm * hd * hd
+    res["linattn_scan prefill (chunk)"] = {"us": round(t_new * 1e6, 1), "frac_of_fp32_fma": round(wl / t_new / fma_peak, 3),
+                                           "like": "mlstm_scan prefill (chunk)", "like_us": round(t_like * 1e6, 1),
+                                           "like_frac": round(wl / t_like / fma_peak, 3), "distance_ratio": round(t_new / t_like, 2)}
+    log(f"  linattn_scan prefill (chunk)       {t_new * 1e6:9.1f} us  {wl / t_new / fma_peak:6.3f} of fp32 FMA | mlstm_scan: "
+        f"{t_like * 1e6:9.1f} us {wl / t_like / fma_peak:6.3f}  -> {t_new / t_like:5.2f}x as far")
+    cud, ctxd = i32(np.arange(B + 1)), i32(np.full(B, ctx))
+    xB, orB, pmB, gatesB = x32l[:B], o_raw[:B], pm[:B], gates[:B]
+    t_new = _time(lambda: ops.linattn_scan(xB, 0, kcl, vcl, decay, cud, ctxd, slot_b, Sst, orB, Hm, hd, hd), flush)
+    t_like = _time(lambda: ops.mlstm_scan(pmB, 0, Hm * hd, 2 * Hm * hd, gatesB, gb, cud, ctxd, slot_b, Sm, nst, mst, orB, Hm, hd, hd,
+                                          15.0), flush)
+    put("linattn_scan decode", t_new, B * Hm * hd * hd * 8.0, "mlstm_scan decode", t_like, B * Hm * hd * hd * 8.0, "bytes")
+    mo = torch.empty(T, Hm * hd, device=dev, dtype=bf)
+    nw = rnd(Hm * hd)
+    t_new = _time(lambda: ops.linattn_out(o_raw, pl, 3 * Hm * hd, nw, mo, Hm, hd, 1e-5, True, "sigmoid"), flush)
+    t_like = _time(lambda: ops.mlstm_out(o_raw, pm, 3 * Hm * hd, nw, mo, Hm, hd, 1e-5), flush)
+    put("linattn_out (all heads)", t_new, T * Hm * hd * 8.0, "mlstm_out", t_like, T * Hm * hd * 8.0, "bytes")
+    t_new = _time(lambda: ops.linattn_out(o_raw, pl, 3 * Hm * hd, None, mo, Hm, hd, 1e-5, False, "silu"), flush)
+    put("linattn_out (per head)", t_new, T * Hm * hd * 8.0, "mlstm_out", t_like, T * Hm * hd * 8.0, "bytes")
+
+    # ---- sigmoid-routed experts weighted on their input vs the Mixtral path at equal sizes
+    xin = rnd(T, D)
+    for rows, tag in ((T, "prefill"), (B, "decode")):
+        rws = ops.RoutedWorkspace(rows, top, E, D, ffe, bf, dev)
+        router = torch.zeros(128, D, device=dev, dtype=bf)
+        router[:E] = rnd(E, D, sc=0.05)
+        w13 = rnd(E * 2 * ffe, D, sc=0.02)
+        w2 = rnd(E * D, ffe, sc=0.02)
+        xr_ = xin[:rows]
+        yo = torch.empty(rows, D, device=dev, dtype=f32)
+        t_new = _time(lambda: ops.routed_experts(xr_, router, None, w13, w2, rws, yo, E, 0, top, 1.0, ffe, 0.0, sigmoid=True,
+                                                 renormalize=False, weight_on="input", act="silu"), flush, iters=5, warm=2)
+        mws = ops.MoEWorkspace(rows, top, E, D, ffe, dev)
+        rl = rnd(rows, ops.ROUTER_PAD)
+        rw_ = ops.pad_router(router[:E].contiguous())
+        ybf = torch.empty(rows, D, device=dev, dtype=bf)
+
+        def like():
+            ops.gemm(xr_, rw_, out=rl)
+            ops.moe_experts(xr_, rl, w13, w2, top, mws, out=ybf)
+
+        t_like = _time(like, flush, iters=5, warm=2)
+        put(f"routed experts ({tag})", t_new, 6.0 * rows * top * D * ffe, f"Mixtral experts ({tag})", t_like,
+            6.0 * rows * top * D * ffe, "flops")
+        del rws, mws
+    return res
+
+
+FAMILIES = {"vodavik": (vodavik_config, _kernel_numbers), "danipel": (danipel_config, _kernel_numbers_danipel),
+            "resevik": (resevik_config, _kernel_numbers_resevik)}
+# a family whose closest existing model is another layer-list design is measured beside that one too
+CLOSEST = {"resevik": ("vodavik", vodavik_config)}
 
 
 def run(sizes=("2k", "4k"), seqs=4, prompt=2048, batch=64, decode_steps=32, log=None, family="vodavik"):
@@ -449,7 +642,10 @@ def run(sizes=("2k", "4k"), seqs=4, prompt=2048, batch=64, decode_steps=32, log=
     for size in sizes:
         log(f"size {size}: {SIZES[size]}")
         o = {"model": {}, "kernels": {}}
-        for name, cfg in ((family, make(size)), ("llama", llama_config(size))):
+        models = [(family, make(size)), ("llama", llama_config(size))]
+        if family in CLOSEST:
+            models.insert(1, (CLOSEST[family][0], CLOSEST[family][1](size)))
+        for name, cfg in models:
             o["model"][name] = _model_numbers(cfg, seqs, prompt, batch, decode_steps, log)
         o["kernels"] = kernels(size, seqs * prompt, batch, prompt, log)
         out["sizes"][size] = o

@@ -143,14 +143,16 @@ def test_residual_sum_of_up_to_three_addends_and_rms_norm(D, xdt):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("H,G,dk,dims", [(4, 2, 10, 6), (6, 3, 64, 32), (2, 2, 128, 128), (3, 1, 7, 2)])
-def test_rotation_unit_norm_and_cache_rows_of_an_attention_whose_values_are_its_keys(dtype, H, G, dk, dims):
+@pytest.mark.parametrize("H,G,dk,dims,pad", [(4, 2, 10, 6, 3), (6, 3, 64, 32, 3), (6, 3, 64, 32, 16), (2, 2, 128, 128, 0),
+                                                 (3, 1, 7, 2, 0), (16, 2, 128, 64, 0), (5, 5, 32, 16, 8)])
+def test_rotation_unit_norm_and_cache_rows_of_an_attention_whose_values_are_its_keys(dtype, H, G, dk, dims, pad):
     """Interleaved pairs, positions far from 0 (the angle must not lose digits), shuffled cache slots, a padding row:
-    q in place, rotated and normed keys in the K pages, the keys as projected in the V pages."""
+    q in place, rotated and normed keys in the K pages, the keys as projected in the V pages.  Rows whose pitch is a
+    multiple of 16 bytes take the 16-byte kernel, the others the element-wise one."""
     from gpustack_b200 import ops
 
     T, page, blocks, eps, base = 11, 16, 5, 1e-5, 5e5
-    proj = _rnd(T, (H + G) * dk + 3, seed=1, dtype=dtype)
+    proj = _rnd(T, (H + G) * dk + pad, seed=1, dtype=dtype)
     pos = torch.tensor([0, 1, 2, 39, 40, 1000, 4095, 65537, 200001, 7, 8], dtype=torch.int32)
     slots = torch.randperm(blocks * page, generator=torch.Generator().manual_seed(2))[:T].to(torch.int32)
     slots[4] = -1
@@ -179,11 +181,15 @@ def test_rotation_unit_norm_and_cache_rows_of_an_attention_whose_values_are_its_
 
 
 @pytest.mark.parametrize("src", [torch.float32, BF])
-@pytest.mark.parametrize("feature,dims,half", [("silu", 0, False), (None, 12, True), (None, 8, True), ("silu", 4, False)])
-def test_feature_map_rotation_and_key_factor_into_fp32_rows(src, feature, dims, half):
+@pytest.mark.parametrize("feature,dims,half", [("silu", 0, False), (None, 12, True), (None, 8, True), ("silu", 4, False),
+                                               (None, 32, True), (None, 16, True), ("silu", 16, False)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 12, 10), (3, 32, 16), (8, 128, 128)])
+def test_feature_map_rotation_and_key_factor_into_fp32_rows(src, feature, dims, half, H, dk, dv):
     from gpustack_b200 import ops
 
-    T, H, dk, dv, base = 7, 3, 12, 10, 300.0
+    if dims > dk:
+        pytest.skip("rotation wider than the head")
+    T, base = 7, 300.0
     kc, vc = H * dk, 2 * H * dk
     proj = _rnd(T, vc + 2 * H * dv, seed=3, dtype=src)
     pos = torch.tensor([0, 1, 5, 77, 1023, 30000, 123457], dtype=torch.int32)
