@@ -232,6 +232,136 @@ linattn_chunk_kernel(const float* __restrict__ x, int64_t ld, int q_col, int k_c
   }
 }
 
+// The chunk form for key widths that are multiples of 4 (every real head): register tiles and 16-byte shared loads.
+//   * queries are staged transposed, qT [dk][16 rows] (pitch 20), keys row-major with a pitch that keeps 16-byte alignment;
+//   * S_0^T q_t: a thread owns one state column, FOUR rows of the chunk and a quarter of the key range -- one state
+//     element and one 16-byte query load feed four FMAs; the four key-range quarters meet in shared memory;
+//   * the state update: a thread owns FOUR key rows of one column -- one value and one 16-byte key load per chunk row
+//     feed four FMAs;
+//   * the next chunk's inputs travel in registers while this one is computed.
+constexpr int kL4Pre = 8;            // 16 * dk / 512 elements of q and of k per thread: dk <= 256
+constexpr int kL4QP = 20;            // pitch of qT
+
+__global__ void __launch_bounds__(kLcThreads)
+linattn_chunk4_kernel(const float* __restrict__ x, int64_t ld, int q_col, int k_col, int v_col,
+                      const float* __restrict__ decay, const int32_t* __restrict__ cu_seq,
+                      const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, float* S_state,
+                      float* __restrict__ o_raw, int H, int dk, int dv) {
+  extern __shared__ __align__(16) float smem[];
+  const int kst = dk + 4;
+  float* Ssm = smem;                                  // [dk][33]
+  float* qT = Ssm + ((dk * 33 + 3) & ~3);             // [dk][20]
+  float* ks = qT + dk * kL4QP;                        // [16][dk + 4]
+  float* vs = ks + kLcTok * kst;                      // [16][32]
+  float* part = vs + kLcTok * 32;                     // [4][16][32]
+  float* A = part + 4 * kLcTok * 32;                  // [16][17]
+  float* dp = A + kLcTok * 17;                        // [17]
+  const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+  const int slot = state_slots[s];
+  if (slot < 0) return;
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (t1 <= t0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c0 = z * 32;
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
+  const bool fresh = ctx_lens[s] == 0;
+  for (int i = tid; i < dk * 32; i += kLcThreads) {
+    const int c = i / dk, r = i - c * dk;
+    Ssm[r * 33 + c] = (!fresh && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + r] : 0.f;
+  }
+  for (int i = tid; i < dk * kL4QP; i += kLcThreads) qT[i] = 0.f;     // rows of a short last chunk stay finite
+  if (tid <= kLcTok) dp[tid] = (float)pow((double)decay[h], (double)tid);
+  float rq[kL4Pre], rk[kL4Pre], rv = 0.f;
+  auto fetch = [&](int ch, int nt) {
+#pragma unroll
+    for (int u = 0; u < kL4Pre; ++u) {
+      const int i = tid + u * kLcThreads;
+      if (i < nt * dk) {
+        const int tt = i / dk, d = i - tt * dk;
+        const float* row = x + (size_t)(ch + tt) * ld;
+        rq[u] = row[q_col + h * dk + d];
+        rk[u] = row[k_col + h * dk + d];
+      }
+    }
+    const int tt = tid >> 5, c = c0 + (tid & 31);
+    rv = (tt < nt && c < dv) ? x[(size_t)(ch + tt) * ld + v_col + h * dv + c] : 0.f;
+  };
+  fetch(t0, min(kLcTok, t1 - t0));
+  for (int ch = t0; ch < t1; ch += kLcTok) {
+    const int nt = min(kLcTok, t1 - ch);
+    __syncthreads();                                  // state update of the previous chunk done, inputs free
+#pragma unroll
+    for (int u = 0; u < kL4Pre; ++u) {
+      const int i = tid + u * kLcThreads;
+      if (i < nt * dk) {
+        const int tt = i / dk, d = i - tt * dk;
+        qT[d * kL4QP + tt] = rq[u];
+        ks[tt * kst + d] = rk[u];
+      }
+    }
+    vs[tid] = rv;
+    if (ch + kLcTok < t1) fetch(ch + kLcTok, min(kLcTok, t1 - ch - kLcTok));
+    __syncthreads();
+    // (a) k_s . q_t for s <= t
+    if (tid < 256) {
+      const int t = tid >> 4, sx = tid & 15;
+      if (t < nt && sx <= t) {
+        float acc = 0.f;
+        const float* kr = ks + sx * kst;
+        for (int r = 0; r < dk; ++r) acc = fmaf(kr[r], qT[r * kL4QP + t], acc);
+        A[t * 17 + sx] = acc;
+      }
+    }
+    // (b) S_0^T q_t: column = lane, rows 4 tg .. 4 tg + 3, key range quarter rq_
+    {
+      const int tg = warp & 3, rq_ = warp >> 2;
+      const int r_lo = (dk * rq_) >> 2, r_hi = (dk * (rq_ + 1)) >> 2;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int r = r_lo; r < r_hi; ++r) {
+        const float sv = Ssm[r * 33 + lane];
+        const float4 q4 = *reinterpret_cast<const float4*>(qT + r * kL4QP + tg * 4);
+        a0 = fmaf(sv, q4.x, a0);
+        a1 = fmaf(sv, q4.y, a1);
+        a2 = fmaf(sv, q4.z, a2);
+        a3 = fmaf(sv, q4.w, a3);
+      }
+      float* pp = part + ((rq_ * kLcTok + tg * 4) * 32) + lane;
+      pp[0] = a0; pp[32] = a1; pp[64] = a2; pp[96] = a3;
+    }
+    __syncthreads();
+    // outputs: thread = (row = warp, column = lane); the quarters are added in a fixed order
+    if (warp < nt) {
+      const int t = warp;
+      const float acc = (part[(0 * kLcTok + t) * 32 + lane] + part[(1 * kLcTok + t) * 32 + lane]) +
+                        (part[(2 * kLcTok + t) * 32 + lane] + part[(3 * kLcTok + t) * 32 + lane]);
+      float num = dp[t + 1] * acc;
+      for (int sx = 0; sx <= t; ++sx) num = fmaf(dp[t - sx] * A[t * 17 + sx], vs[sx * 32 + lane], num);
+      if (c0 + lane < dv) o_raw[(size_t)(ch + t) * H * dv + h * dv + c0 + lane] = num;
+    }
+    // (c) state update: S[r .. r+3][c] = d^n S + sum_s d^{n-1-s} k_s[r .. r+3] v_s[c]
+    for (int it = tid; it < (dk >> 2) * 32; it += kLcThreads) {
+      const int r = (it >> 5) << 2, c = it & 31;
+      const float dn = dp[nt];
+      float s0 = dn * Ssm[r * 33 + c], s1 = dn * Ssm[(r + 1) * 33 + c], s2 = dn * Ssm[(r + 2) * 33 + c],
+            s3 = dn * Ssm[(r + 3) * 33 + c];
+      for (int sx = 0; sx < nt; ++sx) {
+        const float v = dp[nt - 1 - sx] * vs[sx * 32 + c];
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + sx * kst + r);
+        s0 = fmaf(k4.x, v, s0);
+        s1 = fmaf(k4.y, v, s1);
+        s2 = fmaf(k4.z, v, s2);
+        s3 = fmaf(k4.w, v, s3);
+      }
+      Ssm[r * 33 + c] = s0; Ssm[(r + 1) * 33 + c] = s1; Ssm[(r + 2) * 33 + c] = s2; Ssm[(r + 3) * 33 + c] = s3;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * 32; i += kLcThreads) {
+    const int c = i / dk, r = i - c * dk;
+    if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + r] = Ssm[r * 33 + c];
+  }
+}
+
 // ------------------------------------------------------------------------------------------- out
 // One CTA per row.  all_heads: the H * dv outputs are normed together and multiplied by w; otherwise every head is
 // divided by its own root mean square (w optional, dv entries shared by the heads).  gate_act 0 sigmoid, 1 silu.
@@ -284,8 +414,18 @@ extern "C" int b200_linattn_scan(const float* x, int64_t ld, int q_col, int k_co
   cudaStream_t s = (cudaStream_t)stream;
   const int Z = (dv + kLaCols - 1) / kLaCols;
   dim3 grid(n_seqs, H, Z);
-  if (max_len > 2) {
+  if (max_len > 2 && dk % 4 == 0) {
     // prompt portions: the chunk form (a single decode row riding in the same launch is a chunk of one)
+    const size_t smem4 = sizeof(float) * ((((size_t)dk * 33 + 3) & ~(size_t)3) + (size_t)dk * kL4QP + (size_t)kLcTok * (dk + 4) +
+                                          kLcTok * 32 + 4 * kLcTok * 32 + kLcTok * 17 + 32);
+    if (smem4 > 48 * 1024)
+      cudaFuncSetAttribute(linattn_chunk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4);
+    linattn_chunk4_kernel<<<grid, kLcThreads, smem4, s>>>(x, ld, q_col, k_col, v_col, decay, cu_seq, ctx_lens, state_slots, S,
+                                                          o_raw, H, dk, dv);
+    return b200_check_launch("b200_linattn_scan(chunk4)");
+  }
+  if (max_len > 2) {
+    // key widths that are not multiples of 4: the element-wise chunk kernel
     const size_t smem = sizeof(float) * ((size_t)dk * 33 + 2 * (size_t)kLcTok * (dk + 1) + kLcTok * 32 + kLcTok * 17 + 32);
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(linattn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
