@@ -545,6 +545,60 @@ def test_mixed_batches_of_unequal_requests_with_reused_pages_and_slots(model, dt
     assert eng.runner.stats.get("mixed_steps", 0) >= 4 and eng.runner.stats["decode_steps"] >= 1
 
 
+def _random_cfg(rng):
+    """A random model: layer kinds, order, head counts, widths (odd and tile-sized), windows, decays, rotations,
+    experts and the repeated span all drawn anew."""
+    D = rng.choice([48, 64, 96, 128, 192, 256, 320])
+    n = rng.randint(2, 6)
+    layers = []
+    for _ in range(n):
+        kind = rng.choice(["attention", "retention", "lightning"])
+        if kind == "attention":
+            G = rng.choice([1, 2, 3, 4])
+            dk = rng.choice([8, 16, 20, 24, 32, 64, 128])
+            layer = _attn(G * rng.choice([1, 2, 3, 4, 5]), G, dk, rng.choice([1, 2, 5, 16, 17, 33, 48, 64, 100, 1000]),
+                          dims=rng.choice([d for d in (2, 4, 8, 16, 32, 64, 128) if d <= dk]), base=rng.choice([100.0, 1e4, 3e5]),
+                          scale=rng.choice([dk ** -0.5, 0.2]))
+        else:
+            H, dk, dv = rng.choice([1, 2, 3, 4, 6]), rng.choice([8, 12, 16, 20, 32, 64, 128]), rng.choice([8, 12, 16, 32, 40, 64, 128])
+            layer = _lin(kind, H, dk, dv, [rng.choice([0.3, 0.6, 0.9, 0.99, 0.9985, 1.0]) for _ in range(H)],
+                         dims=rng.choice([d for d in (2, 4, 8, 16, 32, 64, 128) if d <= dk]), base=rng.choice([100.0, 1e4, 1e6]))
+        E = rng.choice([1, 2, 4, 8, 16])
+        layers.append(dict(layer, mlp=_moe(E, rng.randint(1, min(E, 4)), rng.choice([16, 24, 64, 96, 128, 256])) if rng.random() < 0.8 else None))
+    a = rng.randint(0, n)
+    return {"architecture": "Resevik", "vocab": rng.choice([100, 257, 1000]), "width": D, "embedding": {"scale": rng.choice([1.0, D ** 0.5])},
+            "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers,
+            "loop": {"start": a, "stop": rng.randint(a, n), "times": rng.choice([1, 2, 3])}}
+
+
+@pytest.mark.parametrize("seed", [101, 102, 103, 104, 105, 106])
+def test_random_configurations_in_float32(seed):
+    """Whole prompt, and two requests in portions beside single tokens, against the oracle (fp32: no router call is
+    close enough for rounding to overturn it)."""
+    import random
+
+    cfg = _random_cfg(random.Random(seed))
+    W = O.random_weights(cfg, seed=seed)
+    t1, t2 = _tokens(cfg, 150, seed), _tokens(cfg, 70, seed + 1)
+    w1, w2 = O.forward(cfg, W, t1), O.forward(cfg, W, t2)
+    eng = _engine(cfg, W, "float32", blocks=20)
+    assert _rel(eng.replay_step([("a", t1, list(range(150)))], ["a"]), w1) < TOL["float32"]
+    toks, at, got = {"x": t1, "y": t2}, {"x": 0, "y": 0}, {"x": [], "y": []}
+    for step in ([("x", 37), ("y", 2)], [("x", 2), ("y", 30)], [("x", 1), ("y", 1)], [("x", 64), ("y", 1)], [("x", 1), ("y", 36)], [("x", 45)]):
+        entries, end = [], []
+        for rid, n in step:
+            entries.append((rid, toks[rid][at[rid]:at[rid] + n], list(range(n))))
+            at[rid] += n
+            if at[rid] == len(toks[rid]):
+                end.append(rid)
+        out, off = eng.replay_step(entries, end), 0
+        for rid, n in step:
+            got[rid].append(out[off:off + n])
+            off += n
+    assert _rel(np.concatenate(got["x"]), w1) < TOL["float32"] and _rel(np.concatenate(got["y"]), w2) < TOL["float32"]
+    assert eng.sched.pool.num_free == eng.sched.pool.num_total
+
+
 def test_long_decoding_through_the_graphs_in_float32():
     """300 single-token steps after a short prompt through the captured decode graphs: every window slides over
     decoded tokens many times, the decode kernel walks 20 pages, the recurrent states pass through 300 updates."""
