@@ -399,10 +399,11 @@ def _run_window_tc(q, kc, vc, perm, H, G, dk, window, scale, start, n, splits):
 
 @pytest.mark.parametrize("window,n,start,splits", [(40, 300, 0, 1), (64, 300, 33, 3), (65, 257, 64, 2), (200, 300, 100, 4),
                                                    (1, 130, 7, 1), (1000, 300, 0, 2), (129, 400, 250, 8)])
-def test_sliding_window_on_the_tensor_core_attention_kernels(window, n, start, splits):
-    """128-wide heads in groups of four, bf16: the tcgen05 prefill kernel skips the key blocks before a tile's window
-    and masks inside the first one; the split-KV decode kernel divides only the window's pages among its splits."""
-    H, G, dk, scale = 8, 2, 128, 0.09
+@pytest.mark.parametrize("H,G", [(8, 2), (8, 1)])
+def test_sliding_window_on_the_tensor_core_attention_kernels(window, n, start, splits, H, G):
+    """128-wide heads in groups of four and eight, bf16: the tcgen05 prefill kernel skips the key blocks before a tile's
+    window and masks inside the first one; the split-KV decode kernel divides only the window's pages among its splits."""
+    dk, scale = 128, 0.09
     q, k, v, kc, vc, perm = _window_case(BF, n, H, G, dk, window, seed=17)
     want = O.window_softmax_attention(q.to(F64), k.to(F64), v.to(F64), scale, window).reshape(n, -1)
     out, od = _run_window_tc(q, kc, vc, perm, H, G, dk, window, scale, start, n, splits)
