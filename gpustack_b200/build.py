@@ -38,6 +38,9 @@ SOURCES = [
     "prenorm.cu",
     "rot_prep.cu",
     "linear_attn.cu",
+    "sandwich.cu",
+    "gated_recurrence.cu",
+    "gated_linear_attn.cu",
 ]
 # What a layer-list decoder (attention with a softmax sink / matrix-memory recurrence, norm after the
 # sum) launches: a fresh checkout that only serves such a model compiles these and nothing else.
@@ -81,8 +84,28 @@ PARALLEL_SOURCES = [
 ]
 
 
+# What a decoder with a norm before and after every sublayer, input convolutions, rotary attention (also with pooled
+# blocks beside a window), gated diagonal recurrences and gated linear attention launches
+SANDWICH_SOURCES = [
+    "runtime.cu",
+    "elementwise.cu",
+    "gemm_tcgen05.cu",
+    "gemm_simt.cu",
+    "gemm_simt_grouped.cu",
+    "sandwich.cu",
+    "rot_prep.cu",
+    "attention_sink.cu",
+    "linear_attn.cu",
+    "gated_recurrence.cu",
+    "gated_linear_attn.cu",
+]
+
+
 def layer_list_sources(mcfg):
     """(tag, sources) of the library a process serving this layer-list model needs."""
+    if getattr(mcfg, "residual", "post_ln") == "sandwich":
+        tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)
+        return ("sandwich_tc", SANDWICH_SOURCES + ATTENTION_TC_SOURCES) if tc else ("sandwich", list(SANDWICH_SOURCES))
     if getattr(mcfg, "residual", "post_ln") == "parallel":
         routed = any(l.mlp is not None and l.mlp.kind == "moe" for l in mcfg.layers)
         tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)

@@ -15,7 +15,7 @@ from typing import Optional
 
 SUPPORTED_ARCHS = ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM")
 # designs whose config.json lists their layers one by one (LayerListConfig below)
-LAYER_LIST_ARCHS = ("Vodavik", "Danipel", "Resevik")
+LAYER_LIST_ARCHS = ("Vodavik", "Danipel", "Resevik", "Dotorax")
 
 
 @dataclass
@@ -233,6 +233,11 @@ class AttentionSpec:
     qk_unit_norm: bool = False     # q and k over their root mean square per head AFTER the rotation, no weight
     window: int = 0                # > 0: position i sees j with 0 <= i - j < window
     values_are_keys: bool = False  # no value projection: v = k as projected (before rotation and norm); vdim == dim
+    gate_per_head: bool = False    # the output gate is ONE number per head (gate projection [heads, width])
+    head_temp: bool = False        # a learned factor per head on the score (tensor `temp` [heads])
+    # pool > 0 (with a window): beside the window's tokens, position i sees one (mean key, mean value) per block
+    # [b pool, (b + 1) pool) that lies wholly before the window, (b + 1) pool - 1 <= i - window, in the same softmax
+    pool: int = 0
 
     kind = "attention"
 
@@ -244,7 +249,19 @@ class AttentionSpec:
     def tile_sized(self) -> bool:
         """Keys and values share one width that is a tensor-core tile (64 / 128) and the group fits the decode
         kernel: the Llama-class attention kernels (with sink and gate) can serve this mixer in bf16."""
-        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
+        return (self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
+                and not self.pool and not (self.gate and self.gate_per_head))
+
+    @property
+    def gate_width(self) -> int:
+        """Rows of the gate projection."""
+        return 0 if not self.gate else (self.heads if self.gate_per_head else self.out_width)
+
+    @property
+    def pool_per_page(self):
+        """(pooled entries a KV page can own) as a function of the page size: entry b lives in the page of its
+        FIRST token, so a page of n tokens owns at most ceil(n / pool) entries."""
+        return lambda page: -(-page // self.pool) if self.pool else 0
 
     @property
     def out_width(self) -> int:
@@ -294,6 +311,70 @@ class LinearAttentionSpec:
     def proj_rows(self) -> int:
         """Rows of the fused projection [q | k | v | gate]."""
         return 2 * self.heads * self.dim + 2 * self.out_width
+
+
+@dataclass
+class GatedRecurrenceSpec:
+    """Gated diagonal linear recurrence (a real-gated linear recurrent unit) with a short convolution in front.  Two
+    branches of `width` channels read the mixer input: y = gelu_tanh(W_y h + b_y) and u = conv(W_x h + b_x) (causal,
+    per channel, `conv` taps, with a bias).  The channels are cut into `blocks` equal parts with one square matrix per
+    part and gate: r = sigmoid(A u + a), i = sigmoid(B u + b); decay = exp(-gate_c r softplus(lam));
+    S_t = decay S_(t-1) + sqrt(1 - decay^2) i u, S = 0 before the first token; output W_o (S * y)."""
+    width: int
+    blocks: int
+    conv: int                      # taps of the convolution (the last one multiplies the current token)
+    gate_c: float = 8.0
+
+    kind = "gated_recurrence"
+
+    @property
+    def out_width(self) -> int:
+        return self.width
+
+    @property
+    def proj_rows(self) -> int:
+        """Rows of the projection [y | x]."""
+        return 2 * self.width
+
+
+@dataclass
+class SideBySideSpec:
+    """Two mixers that read the same input; the mixer's output is left_scale * left + right_scale * right."""
+    left: "AttentionSpec"
+    right: GatedRecurrenceSpec
+    left_scale: float
+    right_scale: float
+
+    kind = "side_by_side"
+
+    @property
+    def out_width(self) -> int:
+        return self.left.out_width + self.right.out_width
+
+
+@dataclass
+class GatedLinearAttentionSpec:
+    """Linear attention whose state rows decay at a data-dependent rate per key channel: per head
+    S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q scaled by dim^(-1/2) and
+    alpha = sigmoid(z)^(1/tau), z = A2 (A1 h) + b (a low-rank projection; its rank is the checkpoint's, decay_rank is
+    what a randomly initialised model gets).  Every head's output is RMS-normed with one weight vector of vdim
+    entries shared by the heads, multiplied by silu(G h) and projected."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    decay_rank: int = 16
+
+    kind = "gated_linear_attention"
+
+    @property
+    def out_width(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def proj_rows(self) -> int:
+        """Rows of the fused projection [q | k | v | gate | decay latent]."""
+        return 2 * self.heads * self.dim + 2 * self.out_width + self.decay_rank
 
 
 @dataclass
@@ -405,8 +486,11 @@ class MoESpec:
 class MLPSpec:
     kind: str                      # "dense" | "moe"
     ff: int                        # dense: hidden width; moe: the widest hidden width (expert or shared)
-    act: str = "relu2"             # dense: "relu2" = down(relu(up x)^2); "gelu_tanh" = down(gelu(gate x) * up x)
+    act: str = "relu2"             # dense: "relu2" = down(relu(up x)^2); "gelu_tanh" = down(gelu(gate x) * up x);
+    #                                "clamped_swish" = down(g sigmoid(1.702 g) (u + 1)), g = min(gate x, limit),
+    #                                u = clamp(up x, -limit, limit)
     moe: Optional[MoESpec] = None
+    limit: float = 0.0
 
 
 @dataclass
@@ -432,8 +516,16 @@ class LayerListConfig:
     # x_t <- sum_s mix[s, t] x_s + residual_mult * out[t] * y; streams == 0: one stream, x <- x + residual_mult * y)
     # "parallel": pre-norm with ONE norm per layer whose output feeds the mixer and the feed-forward side by side,
     # x <- x + mixer(norm(x)) + ff(norm(x))
+    # "sandwich": a norm before and after every sublayer, x <- x + residual_mult * norm_b(f(norm_a(x)))
     residual: str = "post_ln"
-    norm: str = "layernorm"                    # "layernorm" (bias-free) | "tanh": tanh(alpha x) w + b, no statistics | "rms"
+    # "layernorm" (bias-free) | "tanh": tanh(alpha x) w + b, no statistics | "rms" | "rms_zero_centred": an RMS norm
+    # whose stored weight is the deviation from one, x / rms(x) * (1 + w)
+    norm: str = "layernorm"
+    # input convolution: every sublayer reads h + conv(h) instead of its normed input h -- a causal convolution over
+    # time with canon_taps taps per channel (the last tap multiplies the current token); 0 = none.  The last
+    # canon_taps - 1 inputs of every sublayer are part of a sequence's state.
+    canon_taps: int = 0
+    learned_positions: bool = False            # x_0 = embed[token] + pos[position] (table of max_position_embeddings rows)
     # layers loop_start .. loop_stop-1 run loop_times times in a row with the same weights (every pass with its own
     # cache / state); before each pass but the first the embedding output is added to the residual
     loop_start: int = 0
@@ -472,11 +564,14 @@ class LayerListConfig:
     @property
     def has_state(self) -> bool:
         """True when some mixer carries a recurrent state per sequence (needs a state slot; no prefix reuse)."""
-        return any(l.mixer.kind in ("mlstm", "linear_attention") for l in self.layers)
+        return self.canon_taps > 1 or any(l.mixer.kind in ("mlstm", "linear_attention", "side_by_side",
+                                                           "gated_linear_attention") for l in self.layers)
 
     def kv_owner(self, l: int) -> Optional[int]:
         """Layer whose K/V cache layer l's attention reads (itself unless kv_from), None for other mixers."""
         m = self.layers[l].mixer
+        if m.kind == "side_by_side":
+            return l
         if m.kind != "attention":
             return None
         return l if m.kv_from is None else int(m.kv_from)
@@ -488,7 +583,11 @@ class LayerListConfig:
 
     def kv_bytes_per_token(self, tp: int = 1, elem_bytes: int = 2) -> int:
         mixers = [self.layers[l].mixer for l, _ in self.runs()]
+        mixers = [m.left if m.kind == "side_by_side" else m for m in mixers]
         n = sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in mixers if m.kind == "attention" and m.kv_from is None)
+        # pooled block means (fp32): ceil(16 / pool) entries per 16-token page
+        n += sum(m.kv_heads * (m.dim + m.vdim) * 4 * m.pool_per_page(16) // 16 for m in mixers
+                 if m.kind == "attention" and m.pool)
         return n + sum(m.cache_width * elem_bytes for m in mixers if m.kind == "latent_attention")
 
     def state_bytes_per_seq(self) -> int:
@@ -497,17 +596,27 @@ class LayerListConfig:
             if m.kind == "mlstm":
                 z = (m.vdim + 31) // 32
                 n += 4 * m.heads * (m.dim * m.vdim + z * m.dim + z)
-            elif m.kind == "linear_attention":
+            elif m.kind in ("linear_attention", "gated_linear_attention"):
                 n += 4 * m.heads * m.dim * m.vdim
+            elif m.kind == "side_by_side":
+                n += 4 * m.right.width * m.right.conv          # the recurrence and its convolution's last inputs
+        if self.canon_taps > 1:
+            n += 4 * self.hidden_size * (self.canon_taps - 1) * sum(1 + (self.layers[l].mlp is not None) for l, _ in self.runs())
         return n
 
     def weight_bytes(self, tp: int = 1, quantization: Optional[str] = None) -> int:
         D, n = self.hidden_size, 0
         for l in self.layers:
             m = l.mixer
-            if m.kind == "attention":
+            if m.kind == "side_by_side":
+                a, r = m.left, m.right
+                n += D * (a.q_width + a.kv_heads * (a.dim + a.vdim)) + a.out_width * D
+                n += 3 * D * r.width + 2 * r.width * r.width // r.blocks
+            elif m.kind == "gated_linear_attention":
+                n += D * m.proj_rows + m.decay_rank * m.heads * m.dim + m.out_width * D
+            elif m.kind == "attention":
                 kv = 0 if m.kv_from is not None else m.kv_heads * (m.dim + (0 if m.values_are_keys else m.vdim))
-                n += D * (m.q_width + kv + (m.out_width if m.gate else 0)) + m.out_width * D
+                n += D * (m.q_width + kv + m.gate_width) + m.out_width * D
             elif m.kind == "linear_attention":
                 n += D * m.proj_rows + m.out_width * D
             elif m.kind == "latent_attention":
@@ -531,6 +640,8 @@ class LayerListConfig:
             return _danipel_from_dict(d)
         if arch == "Resevik":
             return _resevik_from_dict(d)
+        if arch == "Dotorax":
+            return _dotorax_from_dict(d)
         layers = []
         for i, e in enumerate(d["layers"]):
             mx = e["mixer"]
@@ -571,6 +682,8 @@ class LayerListConfig:
             return _danipel_to_dict(self)
         if self.architecture == "Resevik":
             return _resevik_to_dict(self)
+        if self.architecture == "Dotorax":
+            return _dotorax_to_dict(self)
         out = []
         for l in self.layers:
             m = l.mixer
@@ -747,6 +860,104 @@ def _resevik_to_dict(c: "LayerListConfig") -> dict:
     return {"architecture": "Resevik", "vocab": c.vocab_size, "width": c.hidden_size, "layers": out,
             "norm": {"eps": c.norm_eps}, "embedding": {"scale": c.embed_scale},
             "loop": {"start": c.loop_start, "stop": c.loop_stop, "times": c.loop_times}}
+
+
+def _dotorax_from_dict(d: dict) -> "LayerListConfig":
+    """Dotorax: learned positions added to the embedding; a zero-centred RMS norm before and after every sublayer,
+    x <- x + residual_mult * norm_b(f(norm_a(x))); every sublayer reads its normed input plus a short causal
+    convolution of it; mixers "attention" (grouped softmax attention, half-split rotation, one sigmoid gate per head,
+    optionally on an earlier layer's keys and values), "parallel" (left: sliding-window attention with pooled blocks,
+    interleaved rotation, weightless q / k norm, a temperature per head; right: a gated diagonal recurrence) and "gla"
+    (gated linear attention); a clamped gated feed-forward."""
+    layers = []
+    raw = d["layers"]
+
+    def attention(i, mx, layout, **kw):
+        r = mx["rot"]
+        rot = RotarySpec(dims=int(r["dims"]), base=float(r["base"]), layout=layout)
+        if rot.dims % 2 or rot.dims <= 0 or rot.dims > int(mx["dim"]):
+            raise ValueError(f"layer {i}: rot.dims {rot.dims} must be even and at most dim {mx['dim']}")
+        spec = AttentionSpec(heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])), dim=int(mx["dim"]),
+                             vdim=int(mx.get("vdim", mx["dim"])), scale=float(mx["scale"]), qk_norm=False, qkv_bias=False,
+                             sink=False, rot=rot, **kw)
+        if spec.heads % spec.kv_heads:
+            raise ValueError(f"layer {i}: heads {spec.heads} not a multiple of kv_heads {spec.kv_heads}")
+        return spec
+
+    for i, e in enumerate(raw):
+        mx, kind = e["mixer"], e["type"]
+        if kind == "attention":
+            src = mx.get("kv_from")
+            spec = attention(i, mx, "half", gate=True, gate_per_head=True, kv_from=None if src is None else int(src))
+            if src is not None:
+                o = raw[int(src)] if 0 <= int(src) < i else None
+                if o is None or o["type"] != "attention" or o["mixer"].get("kv_from") is not None:
+                    raise ValueError(f"layer {i}: kv_from must name an earlier attention layer with its own cache")
+                om = o["mixer"]
+                if (int(om["heads"]), int(om.get("kv_heads", om["heads"])), int(om["dim"]), int(om.get("vdim", om["dim"]))) \
+                        != (spec.heads, spec.kv_heads, spec.dim, spec.vdim):
+                    raise ValueError(f"layer {i}: head shapes differ from layer {src}, whose keys and values it reads")
+        elif kind == "parallel":
+            L, R = mx["left"], mx["right"]
+            left = attention(i, L, "interleaved", gate=False, qk_unit_norm=True, head_temp=True,
+                             window=int(L["mask"]["size"]), pool=int(L["mask"]["pool"]))
+            if left.window < 1 or left.pool < 1:
+                raise ValueError(f"layer {i}: mask.size {left.window} and mask.pool {left.pool} must be at least 1")
+            right = GatedRecurrenceSpec(width=int(R["width"]), blocks=int(R["blocks"]), conv=int(R["conv"]))
+            if right.width % right.blocks or right.conv < 1:
+                raise ValueError(f"layer {i}: width {right.width} in {right.blocks} blocks, {right.conv} taps")
+            spec = SideBySideSpec(left=left, right=right, left_scale=float(mx["left_scale"]),
+                                  right_scale=float(mx["right_scale"]))
+        elif kind == "gla":
+            spec = GatedLinearAttentionSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                                            tau=float(mx["tau"]), decay_rank=int(mx.get("decay_rank", 16)))
+            if spec.tau <= 0:
+                raise ValueError(f"layer {i}: tau {spec.tau} must be positive")
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        mlp = e.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind") != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+            mlp = MLPSpec(kind="dense", ff=int(mlp["ff"]), act="clamped_swish", limit=float(mlp["limit"]))
+        layers.append(LayerSpec(mixer=spec, mlp=mlp))
+    taps = int((d.get("canon") or {}).get("taps", 0))
+    if taps < 0:
+        raise ValueError(f"canon.taps {taps}")
+    eos_all = _eos_of(d)
+    return LayerListConfig(architecture="Dotorax", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                           norm_eps=float(d["norm"]["eps"]), residual="sandwich", norm="rms_zero_centred",
+                           residual_mult=float(d.get("residual_mult", 1.0)), canon_taps=taps, learned_positions=True,
+                           max_position_embeddings=int(d["max_positions"]), eos_token_ids=eos_all,
+                           eos_token_id=eos_all[0] if eos_all else None, bos_token_id=d.get("bos_token_id"))
+
+
+def _dotorax_to_dict(c: "LayerListConfig") -> dict:
+    def attention(m):
+        mx = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+              "rot": m.rot.to_dict()}
+        if m.kv_from is not None:
+            mx["kv_from"] = m.kv_from
+        if m.window:
+            mx["mask"] = {"size": m.window, "pool": m.pool}
+        return mx
+
+    out = []
+    for l in c.layers:
+        m = l.mixer
+        if m.kind == "attention":
+            kind, mx = "attention", attention(m)
+        elif m.kind == "side_by_side":
+            kind = "parallel"
+            mx = {"left": attention(m.left), "left_scale": m.left_scale, "right_scale": m.right_scale,
+                  "right": {"width": m.right.width, "blocks": m.right.blocks, "conv": m.right.conv}}
+        else:
+            kind, mx = "gla", {"heads": m.heads, "dim": m.dim, "vdim": m.vdim, "tau": m.tau, "decay_rank": m.decay_rank}
+        mlp = None if l.mlp is None else {"kind": "dense", "ff": l.mlp.ff, "limit": l.mlp.limit}
+        out.append({"type": kind, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Dotorax", "vocab": c.vocab_size, "width": c.hidden_size, "layers": out,
+            "norm": {"eps": c.norm_eps}, "residual_mult": c.residual_mult, "canon": {"taps": c.canon_taps},
+            "max_positions": c.max_position_embeddings}
 
 
 # Named shapes used by tests and bench (random-init; there are no checkpoints offline).

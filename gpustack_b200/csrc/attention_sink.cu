@@ -8,6 +8,11 @@
 //   * keys / values that belong to an earlier layer's cache (the caller passes that cache),
 //   * a sliding window (position i sees j with 0 <= i - j < window; 0 = every earlier key): key blocks that lie
 //     wholly before the window are never read.
+//   * pooled blocks beside a window: one (mean key, mean value) per block of `pool` tokens that lies wholly before
+//     the window -- block b is seen by position i when (b + 1) pool - 1 <= i - window -- in the same softmax as the
+//     window's tokens; the means are fp32 entries of a second cache addressed through the same block table
+//     (sandwich.cu: kv_pool_update),
+//   * an output gate with ONE number per head, and a learned factor per head on the score.
 // Three kernels: `attn_prep` (bias + norms + temperature, in place for q, scatter of k and v into
 // the pages), `prefill` (a tile of 16 query rows of one sequence per CTA, keys staged in shared
 // memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps take
@@ -192,7 +197,8 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
                          const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
                          const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                          const float* __restrict__ sink, TA* out, int64_t ldo, int H, int G, int dk, int dv, int page,
-                         float scale, int64_t v_ld, int window) {
+                         float scale, int64_t v_ld, int window, int gate_per_head, const float* __restrict__ head_scale,
+                         const float* __restrict__ pool_k, const float* __restrict__ pool_v, int pool, int per_page) {
   extern __shared__ float smem[];
   float* Qs = smem;                                   // [16][dk]
   float* Ks = Qs + kPfRows * dk;                      // [32][dk + 1]
@@ -205,6 +211,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
   const int nrows = min(kPfRows, qlen - q0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t* bt = block_table + (size_t)s * max_blocks;
+  if (head_scale != nullptr) scale *= head_scale[h];
 
   for (int i = threadIdx.x; i < kPfRows * dk; i += blockDim.x) {
     const int r = i / dk, d = i - r * dk;
@@ -222,13 +229,26 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
   const int kv_end = ctx + q0 + nrows;                // keys this tile can see: [kv_begin, kv_end)
   // a sliding window: position i sees j with 0 <= i - j < window, so nothing before the first row's window is read
   const int kv_begin = window > 0 ? max(0, ctx + q0 - window + 1) : 0;
-  for (int k0 = kv_begin & ~(kPfKeys - 1); k0 < kv_end; k0 += kPfKeys) {
+  // pooled blocks first (entries [0, blocks the tile's last row sees)), then the tokens; one running softmax
+  const int n_pool = (pool_k != nullptr && window > 0) ? max(0, (kv_end - 1 - window + 1) / pool) : 0;
+  const int pool_span = (n_pool + kPfKeys - 1) & ~(kPfKeys - 1);
+  const int tok_begin = kv_begin & ~(kPfKeys - 1);
+  for (int it = -pool_span; it < kv_end - tok_begin; it += kPfKeys) {
+    const bool pooled = it < 0;
+    const int k0 = pooled ? it + pool_span : tok_begin + it;
     __syncthreads();                                  // previous block's K / V fully consumed (and Qs written)
     // each warp stages 8 keys
     for (int jj = 0; jj < kPfKeys / kPfWarps; ++jj) {
       const int j = warp * (kPfKeys / kPfWarps) + jj;
       const int key = k0 + j;
-      if (key < kv_end) {
+      if (pooled && key < n_pool) {
+        const int pj = (key * pool) / page;
+        const size_t base = ((size_t)bt[pj] * G + g) * per_page + (key - (pj * page + pool - 1) / pool);
+        const float* kp = pool_k + base * dk;
+        const float* vp = pool_v + base * dv;
+        for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = kp[d];
+        for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = vp[d];
+      } else if (!pooled && key < kv_end) {
         const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
         const TA* kp = k_cache + base * dk;
         const TA* vp = v_cache + base * v_ld;
@@ -255,7 +275,8 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
 #pragma unroll
     for (int r = 0; r < kPfRowsPerWarp; ++r) {
       const int qpos = ctx + q0 + warp * kPfRowsPerWarp + r;
-      const bool seen = (k0 + lane) <= qpos && (k0 + lane) < kv_end && (window <= 0 || qpos - (k0 + lane) < window);
+      const bool seen = pooled ? (k0 + lane) < (qpos - window + 1) / pool      // (negative numerators: nothing seen)
+                               : ((k0 + lane) <= qpos && (k0 + lane) < kv_end && (window <= 0 || qpos - (k0 + lane) < window));
       const float sv = seen ? sc[r] * scale : -CUDART_INF_F;
       const float mn = fmaxf(m[r], warp_max(sv));
       float p = 0.f, corr = 1.f;
@@ -298,7 +319,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
       if (d < dv) {
         float o = acc[r][c] * inv;
         if (gate_col >= 0) {
-          const float gv = as_f32(proj[t * ld + gate_col + h * dv + d]);
+          const float gv = as_f32(proj[t * ld + gate_col + (gate_per_head ? h : h * dv + d)]);
           o *= 1.0f / (1.0f + expf(-gv));
         }
         as_store(out + t * ldo + h * dv + d, o);
@@ -319,7 +340,9 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
-                        int H, int G, int dk, int dv, int page, float scale, int64_t v_ld, int window) {
+                        int H, int G, int dk, int dv, int page, float scale, int64_t v_ld, int window, int gate_per_head,
+                        const float* __restrict__ head_scale, const float* __restrict__ pool_k,
+                        const float* __restrict__ pool_v, int pool, int per_page) {
   __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
   extern __shared__ __align__(16) float sm_dyn[];      // [dk (padded to 8)] query, then [warps][dv] partial outputs
   constexpr int E = 16 / (int)sizeof(TA);               // elements per 16-byte load
@@ -330,6 +353,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = seq_lens[b];
   const int32_t* bt = block_table + (size_t)b * max_blocks;
+  if (head_scale != nullptr) scale *= head_scale[h];
   for (int d = threadIdx.x; d < dkp; d += blockDim.x)
     qsm[d] = d < dk ? as_f32(proj[(size_t)b * ld + h * dk + d]) * scale : 0.f;
   __syncthreads();
@@ -340,6 +364,39 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
   // a sliding window: the row at position n - 1 sees keys [n - window, n); the first block read is the one that holds
   // the window's first key
   const int first = window > 0 ? max(0, n - window) : 0;
+  // pooled blocks: the row at position n - 1 sees the blocks that end at or before n - 1 - window
+  const int n_pool = (pool_k != nullptr && window > 0) ? max(0, (n - window) / pool) : 0;
+  for (int k0 = warp * 32; k0 < n_pool; k0 += kDecWarps * 32) {
+    const int key = k0 + lane;
+    const bool live = key < n_pool;
+    size_t base = 0;
+    float sc = -CUDART_INF_F;
+    if (live) {
+      const int pj = (key * pool) / page;
+      base = ((size_t)bt[pj] * G + g) * per_page + (key - (pj * page + pool - 1) / pool);
+      const float* kp = pool_k + base * dk;
+      float a = 0.f;
+      for (int d = 0; d < dk; ++d) a = fmaf(qsm[d], kp[d], a);
+      sc = a;
+    }
+    const float mn = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - mn), p = live ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = mn;
+#pragma unroll
+    for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
+    const int cnt = min(32, n_pool - k0);
+    for (int j = 0; j < cnt; ++j) {
+      const float pj_ = __shfl_sync(0xffffffffu, p, j);
+      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
+      const float* vp = pool_v + (size_t)bj * dv;
+#pragma unroll
+      for (int c = 0; c < kMaxDvPerLane; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) acc[c] = fmaf(pj_, vp[d], acc[c]);
+      }
+    }
+  }
   for (int k0 = (first & ~31) + warp * 32; k0 < n; k0 += kDecWarps * 32) {
     const int key = k0 + lane;
     const bool live = key < n && key >= first;
@@ -401,7 +458,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
     for (int w = 0; w < kDecWarps; ++w) o += sm_acc[w * dv + d];
     o *= inv;
     if (gate_col >= 0) {
-      const float gv = as_f32(proj[(size_t)b * ld + gate_col + h * dv + d]);
+      const float gv = as_f32(proj[(size_t)b * ld + gate_col + (gate_per_head ? h : h * dv + d)]);
       o *= 1.0f / (1.0f + expf(-gv));
     }
     as_store(out + (size_t)b * ldo + h * dv + d, o);
@@ -460,13 +517,16 @@ extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias,
 
 extern "C" int b200_attn_sink_prefill_tile(void) { return kPfRows; }
 
-extern "C" int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                         const void* v_cache, const int32_t* block_table, int max_blocks,
-                                         const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
-                                         const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
-                                         int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
-                                         int window, void* stream) {
+extern "C" int b200_attn_sink_prefill_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                           const void* v_cache, const int32_t* block_table, int max_blocks,
+                                           const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                           const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                           int window, int gate_per_head, const float* head_scale, const float* pool_k,
+                                           const float* pool_v, int pool, int per_page, void* stream) {
   if (v_ld <= 0) v_ld = dv;
+  B200_REQUIRE(pool_k == nullptr || (pool_v != nullptr && window > 0 && pool > 0 && per_page == (page + pool - 1) / pool),
+               "attn_sink_prefill: pooled blocks need a window, both caches and ceil(page / pool) entries per page");
   B200_REQUIRE(v_ld >= dv, "attn_sink_prefill: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(tile_rows > 0 && tile_rows % kPfRows == 0, "attn_sink_prefill: tiles of %d rows (multiples of %d)",
                tile_rows, kPfRows);
@@ -484,13 +544,25 @@ extern "C" int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, 
       cudaFuncSetAttribute(attn_sink_prefill_kernel<TA, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     attn_sink_prefill_kernel<TA, L><<<grid, kPfWarps * 32, smem, s>>>(                                             \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, cu_q,       \
-        ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window);                \
+        ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head,   \
+        head_scale, pool_k, pool_v, pool, per_page);                                                               \
   } while (0)
   const bool wide = dv > 256;
   if (f32) { if (wide) B200_PF(float, 16); else B200_PF(float, 8); }
   else { if (wide) B200_PF(bf16, 16); else B200_PF(bf16, 8); }
 #undef B200_PF
   return b200_check_launch("b200_attn_sink_prefill");
+}
+
+extern "C" int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                         const void* v_cache, const int32_t* block_table, int max_blocks,
+                                         const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                         const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                         int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                         int window, void* stream) {
+  return b200_attn_sink_prefill_pool(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, cu_q, ctx_lens,
+                                     tile_seq, tile_q0, n_tiles, tile_rows, sink, out, ldo, H, G, dk, dv, page, scale, v_ld,
+                                     window, 0, nullptr, nullptr, nullptr, 0, 0, stream);
 }
 
 extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
@@ -504,12 +576,15 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
                                    stream);
 }
 
-extern "C" int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                        const void* v_cache, const int32_t* block_table, int max_blocks,
-                                        const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
-                                        int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
-                                        void* stream) {
+extern "C" int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                          const void* v_cache, const int32_t* block_table, int max_blocks,
+                                          const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                          int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
+                                          int gate_per_head, const float* head_scale, const float* pool_k,
+                                          const float* pool_v, int pool, int per_page, void* stream) {
   if (v_ld <= 0) v_ld = dv;
+  B200_REQUIRE(pool_k == nullptr || (pool_v != nullptr && window > 0 && pool > 0 && per_page == (page + pool - 1) / pool),
+               "attn_sink_decode: pooled blocks need a window, both caches and ceil(page / pool) entries per page");
   B200_REQUIRE(v_ld >= dv, "attn_sink_decode: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvLanes && page > 0,
                "attn_sink_decode: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
@@ -524,15 +599,26 @@ extern "C" int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, i
   if (dv > 256)                                                                                                  \
     attn_sink_decode_kernel<TA, V, 16><<<grid, kDecWarps * 32, smem, s>>>(                                       \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens, \
-        sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window);                                           \
+        sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head, head_scale, pool_k, pool_v,  \
+        pool, per_page);                                                                                         \
   else                                                                                                           \
     attn_sink_decode_kernel<TA, V, 8><<<grid, kDecWarps * 32, smem, s>>>(                                        \
       (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
-      sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window)
+      sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head, head_scale, pool_k, pool_v,    \
+      pool, per_page)
   if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }
   else { if (vec) B200_DEC(bf16, true); else B200_DEC(bf16, false); }
 #undef B200_DEC
   return b200_check_launch("b200_attn_sink_decode");
+}
+
+extern "C" int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                        const void* v_cache, const int32_t* block_table, int max_blocks,
+                                        const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                        int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
+                                        void* stream) {
+  return b200_attn_sink_decode_pool(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, seq_lens, B, sink, out,
+                                    ldo, H, G, dk, dv, page, scale, v_ld, window, 0, nullptr, nullptr, nullptr, 0, 0, stream);
 }
 
 extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,

@@ -14,6 +14,7 @@
 //                 (a softmax-attention mixer), or rows of a separate buffer (a recurrent mixer reads them once);
 //   values        come from their own columns, or are the keys AS PROJECTED (before feature map, rotation and
 //                 norm) when the mixer has no value projection.
+//   A mixer that reads another layer's keys and values passes no key destination: only its queries are prepared.
 // One warp per (token, head slot): slots [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (absent when the
 // values are the keys).  Each lane keeps its entries in registers between the sum of squares and the store.
 // Source type TA (bf16 | fp32), destination type TD (the same, or fp32 for recurrent mixers).
@@ -59,7 +60,7 @@ rot_prep_kernel(RotPrepArgs a) {
   const int hs = blockIdx.y * kRpWarps + (threadIdx.x >> 5);
   const int H = a.H, G = a.G, dk = a.dk, dv = a.dv;
   const bool has_v = a.v_col >= 0;
-  if (hs >= H + G + (has_v ? G : 0)) return;
+  if (hs >= (a.k_out == nullptr ? H : H + G + (has_v ? G : 0))) return;   // no key destination: queries only
   const bool is_q = hs < H, is_k = !is_q && hs < H + G;
   const int g = is_q ? hs : (is_k ? hs - H : hs - H - G);
   const TA* src = reinterpret_cast<const TA*>(a.proj) + (size_t)t * a.ld +
@@ -164,7 +165,7 @@ rot_prep_vec_kernel(RotPrepArgs a, int lph, int items_q, int items_v) {
     __syncthreads();
   }
   const bool has_v = a.v_col >= 0;
-  const int n_slots = H + G + (has_v ? G : 0);
+  const int n_slots = a.k_out == nullptr ? H : H + G + (has_v ? G : 0);    // no key destination: queries only
   const int per_warp = 32 / lph, sub = lane / lph, li = lane % lph;
   const int slot = a.paged ? a.slots[t] : 0;
   const TA* row = reinterpret_cast<const TA*>(a.proj) + (size_t)t * a.ld;
@@ -291,7 +292,7 @@ extern "C" int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_co
   if (T == 0) return B200_OK;
   RotPrepArgs a{proj, ld, q_col, k_col, v_col, positions, slots, q_out, ldq, k_out, ldk, v_out, ldv, paged, page, H, G, dk, dv,
                 feature, dims, half_layout, freq, unit_norm, eps, q_mul, k_mul};
-  const int n_slots = H + G + (v_col >= 0 ? G : 0);
+  const int n_slots = k_out == nullptr ? H : H + G + (v_col >= 0 ? G : 0);
   dim3 grid(T, (n_slots + kRpWarps - 1) / kRpWarps);
   cudaStream_t s = (cudaStream_t)stream;
   {

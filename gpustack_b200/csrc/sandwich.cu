@@ -1,0 +1,262 @@
+// Residual stream with a norm before AND after every sublayer, short causal convolutions with per-sequence state,
+// learned positions, and the block means of a KV cache.  The stream, every statistic and every sum is fp32.
+//
+//   embed_pos        x = table[id] + pos_table[position]                                   (fp32 stream)
+//   sandwich_join    v = ya * y (+ yb * y2)            the sublayer output(s), fp32
+//                    z = x + mult * v / rms(v) * (wb)  the stream takes the NORMED output        (y == null: z = x)
+//                    h = z / rms(z) * (wa)             the next sublayer's normed input, fp32 or rounded once
+//                    rms(v) = sqrt(mean(v^2) + eps); a weight stored around zero enters as 1 + w (zero_centred).
+//                    With a row list it gathers: row r reads row rows[r] and writes h only (the rows whose logits are
+//                    wanted).  One CTA per row, the row staged in shared memory between statistic and product.
+//   causal_conv      out_t = (in_t if add_input) + bias + sum_j w[:, j] in_(t - taps + 1 + j),  zeros before position 0.
+//                    A step brings every sequence's NEW rows; inputs older than the step come from the sequence's
+//                    ring: ring[slot][p mod (taps - 1)][c] holds the input at position p for the last taps - 1
+//                    positions.  A sequence whose context is empty never reads the ring, so a slot needs no clearing.
+//   conv_commit      after the convolution has run: the last taps - 1 inputs of every sequence's new rows go to the
+//                    ring (a separate launch: the convolution's first rows read what the last rows replace).
+//   kv_pool_update   mean key and mean value of every block of `pool` tokens that a step completes, summed in
+//                    position order in fp32 from the cache as it holds them.  Entry b of a sequence lives in the page
+//                    of its first token: pool_k [blocks][G][per_page][dk], entry index b - ceil(first token's page *
+//                    page / pool) -- the sequence's own block table addresses it, and pages that are handed to
+//                    another sequence are overwritten before they are read.
+#include "common.cuh"
+#include "runtime.h"
+#include "../../include/b200.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float sw_f32(float v) { return v; }
+__device__ __forceinline__ float sw_f32(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void sw_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void sw_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__global__ void __launch_bounds__(256)
+embed_pos_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions, const bf16* __restrict__ table,
+                 const bf16* __restrict__ pos_table, float* __restrict__ x, int D, int vocab, int max_pos) {
+  const int t = blockIdx.x;
+  int id = ids[t], p = positions[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+  const bf16* e = table + (size_t)id * D;
+  const bf16* q = pos_table + (size_t)p * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x)
+    x[(size_t)t * D + i] = __bfloat162float(e[i]) + __bfloat162float(q[i]);
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();                                    // red may still be read from the call before
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+sandwich_join_kernel(const float* x_in, const float* __restrict__ y, const float* __restrict__ y2, float ya, float yb,
+                     const bf16* __restrict__ wb, float mult, const int32_t* __restrict__ rows,
+                     const bf16* __restrict__ wa, float* x_out, TO* h_out, int D, float eps, float w_base) {
+  extern __shared__ __align__(16) float zrow[];       // [D] the output row, then the new stream row
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const size_t src = (size_t)(rows != nullptr ? rows[r] : r) * D;
+  if (y != nullptr) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      float v = ya * y[src + i];
+      if (y2 != nullptr) v = fmaf(yb, y2[src + i], v);
+      zrow[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+      zrow[i] = fmaf(mult, zrow[i] * rstd * (w_base + __bfloat162float(wb[i])), x_in[src + i]);
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) zrow[i] = x_in[src + i];
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {    // every thread reads back what it staged itself
+    const float z = zrow[i];
+    if (x_out != nullptr) x_out[(size_t)r * D + i] = z;
+    ss = fmaf(z, z, ss);
+  }
+  if (wa == nullptr || h_out == nullptr) return;
+  const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x)
+    sw_store(h_out + (size_t)r * D + i, zrow[i] * rstd * (w_base + __bfloat162float(wa[i])));
+}
+
+// Row t belongs to the sequence s with cu_seq[s] <= t < cu_seq[s + 1]
+__device__ __forceinline__ int seq_of_row(const int32_t* __restrict__ cu_seq, int n_seqs, int t) {
+  int lo = 0, hi = n_seqs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_seq[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+constexpr int kConvMaxTaps = 8;
+
+// grid (T, ceil(C / 256)); TI input element, TO output element
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __restrict__ in_bias,
+                   const float* __restrict__ w, const float* __restrict__ bias, int add_input,
+                   const float* __restrict__ ring, const int32_t* __restrict__ cu_seq,
+                   const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, int n_seqs, TO* out,
+                   int64_t ld_out, int C, int taps) {
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int s = seq_of_row(cu_seq, n_seqs, t);
+  if (c >= C) return;
+  const int ctx = ctx_lens[s], p = ctx + (t - cu_seq[s]);
+  const int R = taps - 1;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
+  const float cur = sw_f32(in[(size_t)t * ld_in + c]) + ib;
+  float acc = bias != nullptr ? bias[c] : 0.f;
+  if (add_input) acc += cur;
+  const float* wc = w + (size_t)c * taps;
+  for (int j = 0; j < R; ++j) {
+    const int sp = p - R + j;                          // the position tap j multiplies
+    if (sp < 0) continue;
+    float v;
+    if (sp >= ctx) v = sw_f32(in[(size_t)(t - (p - sp)) * ld_in + c]) + ib;
+    else v = ring[((size_t)state_slots[s] * R + (sp % R)) * C + c];
+    acc = fmaf(wc[j], v, acc);
+  }
+  acc = fmaf(wc[R], cur, acc);
+  sw_store(out + (size_t)t * ld_out + c, acc);
+}
+
+// grid (n_seqs, taps - 1, ceil(C / 256))
+template <typename TI>
+__global__ void __launch_bounds__(256)
+conv_commit_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __restrict__ in_bias, float* ring,
+                   const int32_t* __restrict__ cu_seq, const int32_t* __restrict__ ctx_lens,
+                   const int32_t* __restrict__ state_slots, int C, int taps) {
+  const int s = blockIdx.x, r = blockIdx.y, c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int slot = state_slots[s];
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (c >= C || slot < 0 || r >= t1 - t0) return;      // an older input stays where it is
+  const int R = taps - 1;
+  const int p = ctx_lens[s] + (t1 - t0) - 1 - r;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
+  ring[((size_t)slot * R + (p % R)) * C + c] = sw_f32(in[(size_t)(t1 - 1 - r) * ld_in + c]) + ib;
+}
+
+// grid (n_seqs, most blocks a sequence completes in this step, G); cu_q == null: one new row per sequence whose
+// context is ctx_lens[s] - 1 tokens (ctx_lens then counts the new row, as a decode step's lengths do)
+template <typename TA>
+__global__ void __launch_bounds__(128)
+kv_pool_update_kernel(const TA* __restrict__ k_cache, const TA* __restrict__ v_cache, float* pool_k, float* pool_v,
+                      const int32_t* __restrict__ block_table, int max_blocks, const int32_t* __restrict__ cu_q,
+                      const int32_t* __restrict__ ctx_lens, int G, int dk, int dv, int page, int pool, int per_page) {
+  const int s = blockIdx.x, g = blockIdx.z;
+  const int ctx = cu_q != nullptr ? ctx_lens[s] : ctx_lens[s] - 1;
+  const int n = cu_q != nullptr ? cu_q[s + 1] - cu_q[s] : 1;
+  if (n <= 0 || ctx < 0) return;
+  const int b = ctx / pool + blockIdx.y;               // blocks whose last token is among the new rows
+  if (b >= (ctx + n) / pool) return;
+  const int32_t* bt = block_table + (size_t)s * max_blocks;
+  const int first = b * pool, pj = first / page;
+  const int idx = b - (pj * page + pool - 1) / pool;
+  const size_t dst = ((size_t)bt[pj] * G + g) * per_page + idx;
+  const float inv = 1.0f / (float)pool;
+  for (int c = threadIdx.x; c < dk + dv; c += blockDim.x) {
+    const bool is_k = c < dk;
+    const int cc = is_k ? c : c - dk, w = is_k ? dk : dv;
+    const TA* cache = is_k ? k_cache : v_cache;
+    float sum = 0.f;
+    for (int i = 0; i < pool; ++i) {
+      const int tok = first + i;
+      sum += sw_f32(cache[(((size_t)bt[tok / page] * G + g) * page + (tok % page)) * w + cc]);
+    }
+    (is_k ? pool_k : pool_v)[dst * w + cc] = sum * inv;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_embed_pos_f32(const int32_t* ids, const int32_t* positions, const void* table, const void* pos_table,
+                                  float* x, int T, int D, int vocab, int max_pos, void* stream) {
+  B200_REQUIRE(T >= 0 && D > 0 && vocab > 0 && max_pos > 0, "embed_pos: bad shape");
+  if (T == 0) return B200_OK;
+  embed_pos_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(ids, positions, (const bf16*)table, (const bf16*)pos_table, x, D,
+                                                        vocab, max_pos);
+  return b200_check_launch("b200_embed_pos_f32");
+}
+
+extern "C" int b200_sandwich_join(const float* x_in, const float* y, const float* y2, float ya, float yb, const void* wb,
+                                  float mult, const int32_t* rows, const void* wa, float* x_out, void* h_out, int h_f32,
+                                  int T, int D, float eps, int zero_centred, void* stream) {
+  B200_REQUIRE(T >= 0 && D > 0 && x_in != nullptr, "sandwich_join: bad arguments T=%d D=%d", T, D);
+  B200_REQUIRE(y == nullptr || wb != nullptr, "sandwich_join: a sublayer output needs the weight of its norm");
+  B200_REQUIRE(rows == nullptr || x_out == nullptr, "sandwich_join: the gather form writes the normed rows only");
+  if (T == 0) return B200_OK;
+  const size_t smem = (size_t)D * sizeof(float);
+  B200_REQUIRE(smem <= 48 * 1024, "sandwich_join: D=%d exceeds the staged row (12288)", D);
+  cudaStream_t s = (cudaStream_t)stream;
+  const float base = zero_centred ? 1.0f : 0.0f;
+  if (h_f32)
+    sandwich_join_kernel<float><<<T, 256, smem, s>>>(x_in, y, y2, ya, yb, (const bf16*)wb, mult, rows, (const bf16*)wa, x_out,
+                                                     (float*)h_out, D, eps, base);
+  else
+    sandwich_join_kernel<bf16><<<T, 256, smem, s>>>(x_in, y, y2, ya, yb, (const bf16*)wb, mult, rows, (const bf16*)wa, x_out,
+                                                    (bf16*)h_out, D, eps, base);
+  return b200_check_launch("b200_sandwich_join");
+}
+
+extern "C" int b200_causal_conv(const void* in, int in_f32, int64_t ld_in, const float* in_bias, const float* w,
+                                const float* bias, int add_input, const float* ring, const int32_t* cu_seq,
+                                const int32_t* ctx_lens, const int32_t* state_slots, int n_seqs, void* out, int out_f32,
+                                int64_t ld_out, int T, int C, int taps, void* stream) {
+  B200_REQUIRE(T >= 0 && C > 0 && taps >= 1 && taps <= kConvMaxTaps && n_seqs >= 0, "causal_conv: bad shape C=%d taps=%d", C,
+               taps);
+  B200_REQUIRE(taps == 1 || ring != nullptr, "causal_conv: more than one tap needs the sequences' rings");
+  if (T == 0 || n_seqs == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(T, (C + 255) / 256);
+#define B200_CC(TI, TO)                                                                                               \
+  causal_conv_kernel<TI, TO><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, ctx_lens, \
+                                                  state_slots, n_seqs, (TO*)out, ld_out, C, taps)
+  if (in_f32) { if (out_f32) B200_CC(float, float); else B200_CC(float, bf16); }
+  else { if (out_f32) B200_CC(bf16, float); else B200_CC(bf16, bf16); }
+#undef B200_CC
+  return b200_check_launch("b200_causal_conv");
+}
+
+extern "C" int b200_conv_commit(const void* in, int in_f32, int64_t ld_in, const float* in_bias, float* ring,
+                                const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, int n_seqs,
+                                int C, int taps, void* stream) {
+  B200_REQUIRE(C > 0 && taps >= 1 && taps <= kConvMaxTaps && n_seqs >= 0, "conv_commit: bad shape C=%d taps=%d", C, taps);
+  if (n_seqs == 0 || taps == 1) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_seqs, taps - 1, (C + 255) / 256);
+  if (in_f32)
+    conv_commit_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ld_in, in_bias, ring, cu_seq, ctx_lens, state_slots, C, taps);
+  else
+    conv_commit_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ld_in, in_bias, ring, cu_seq, ctx_lens, state_slots, C, taps);
+  return b200_check_launch("b200_conv_commit");
+}
+
+extern "C" int b200_kv_pool_update(const void* k_cache, const void* v_cache, int f32, float* pool_k, float* pool_v,
+                                   const int32_t* block_table, int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                   int n_seqs, int max_new, int G, int dk, int dv, int page, int pool, int per_page,
+                                   void* stream) {
+  B200_REQUIRE(n_seqs >= 0 && G > 0 && dk > 0 && dv > 0 && page > 0 && pool > 0 && per_page == (page + pool - 1) / pool,
+               "kv_pool_update: bad shape page=%d pool=%d per_page=%d", page, pool, per_page);
+  if (n_seqs == 0 || max_new <= 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_seqs, max_new / pool + 1, G);
+  if (f32)
+    kv_pool_update_kernel<float><<<grid, 128, 0, s>>>((const float*)k_cache, (const float*)v_cache, pool_k, pool_v, block_table,
+                                                      max_blocks, cu_q, ctx_lens, G, dk, dv, page, pool, per_page);
+  else
+    kv_pool_update_kernel<bf16><<<grid, 128, 0, s>>>((const bf16*)k_cache, (const bf16*)v_cache, pool_k, pool_v, block_table,
+                                                     max_blocks, cu_q, ctx_lens, G, dk, dv, page, pool, per_page);
+  return b200_check_launch("b200_kv_pool_update");
+}

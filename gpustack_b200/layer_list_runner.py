@@ -1,4 +1,4 @@
-"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik, Danipel, Resevik).
+"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik, Danipel, Resevik, Dotorax).
 
 Same step interface as runner.ModelRunner -- the engine, the scheduler's plans, the staging buffer, CUDA-graph
 decode steps and the sampler are shared -- with this family's layer sequence:
@@ -37,9 +37,21 @@ ONE add_rms_norm launch does the sum and the next norm; "streams": pre-norm over
     embed * scale -> S streams -> per sublayer [ u = sum_s in[s] x_s -> tanh norm -> sublayer ->
                                                  x_t <- sum_s mix[s,t] x_s + m out[t] y ]  -> sum of the streams -> tanh norm
 
-where ONE streams_step launch does a sublayer's write-back and the next sublayer's read + norm.  Feed-forwards:
-relu^2 (ungated), gated GELU, or a routed mixture of clamped gated experts with identity experts and a shared
-expert (ops.routed_experts).
+where ONE streams_step launch does a sublayer's write-back and the next sublayer's read + norm.  "sandwich": a norm before AND after every sublayer,
+
+    embed + learned position -> per sublayer [ x += m * norm_b(output of the sublayer before) ; h = norm_a(x)
+                                               -> h + causal conv(h) (ring of the last inputs per sequence) -> sublayer ]
+          -> x += m * norm_b(last output) -> norm of the wanted rows
+
+where ONE sandwich_join launch does the sum (with the post-norm of the output) and the next pre-norm, and the short
+convolution with its per-sequence ring follows.  Its mixers: rotary attention with one gate per head; a side-by-side
+pair of [sliding-window attention that also sees the pooled blocks before the window | gated diagonal recurrence behind a
+short convolution], whose two output projections meet in the join with their factors; gated linear attention with a
+decay per key channel and token.
+
+Feed-forwards:
+relu^2 (ungated), gated GELU, a clamped gated unit, or a routed mixture of clamped gated experts with identity experts
+and a shared expert (ops.routed_experts).
 
 The residual stream is fp32 from the embedding to the final norm, and so is every sublayer's output on its way
 into the sum (the output projections write fp32); projections read a copy of the stream rounded once to bf16.  With EngineConfig.dtype == "float32" every activation, cache and product is fp32 (CUDA-core GEMM with
@@ -69,7 +81,8 @@ class LayerListRunner(ModelRunner):
         # attention layers whose keys and values have one tile-sized width run on the tensor-core kernels of the
         # Llama-class models (extended with the sink and the gate); the others on the generic kernels
         bf = self.act_dtype == BF16
-        attn = [(l, x.mixer) for l, x in enumerate(cfg.layers) if x.mixer.kind == "attention"]
+        attn = [(l, x.mixer.left if x.mixer.kind == "side_by_side" else x.mixer) for l, x in enumerate(cfg.layers)
+                if x.mixer.kind in ("attention", "side_by_side")]
         self.fast_decode = {l: bf and m.tile_sized for l, m in attn}
         self.fast_prefill = {l: bf and m.tile_sized and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim) for l, m in attn}
         base = ops.attn_sink_prefill_tile()
@@ -84,6 +97,8 @@ class LayerListRunner(ModelRunner):
         self._dec_ws = {}
         self.streams = cfg.residual == "streams"
         self.parallel = cfg.residual == "parallel"
+        self.sandwich = cfg.residual == "sandwich"
+        self.canon_taps = getattr(cfg, "canon_taps", 0)
         self.runs = cfg.runs()                 # [(layer, embedding added before it)]: caches and state belong to a run
         self.looped = any(again for _, again in self.runs)
         self.layer_trace = None                # a list: receives the fp32 residual after every layer run (tests, debugging)
@@ -99,11 +114,16 @@ class LayerListRunner(ModelRunner):
         self.lat_o_width = max([m.heads * m.kv_rank for m in lat] or [0])
         self.routed = [l.mlp.moe for l in cfg.layers if l.mlp is not None and l.mlp.kind == "moe"]
         rec = [l.mixer for l in cfg.layers if l.mixer.kind == "mlstm"]
-        lin = [l.mixer for l in cfg.layers if l.mixer.kind == "linear_attention"]
-        self.gate_width = max([2 * m.heads for m in rec] or [0])
+        lin = [l.mixer for l in cfg.layers if l.mixer.kind in ("linear_attention", "gated_linear_attention")]
+        gla = [l.mixer for l in cfg.layers if l.mixer.kind == "gated_linear_attention"]
+        gdr = [l.mixer.right for l in cfg.layers if l.mixer.kind == "side_by_side"]
+        self.gate_width = max([2 * m.heads for m in rec] + [m.heads * m.dim for m in gla] + [2 * m.width for m in gdr] or [0])
         self.rec_width = max([m.out_width for m in rec + lin] or [0])
-        self.lin_width = max([2 * m.heads * m.dim + m.out_width for m in lin] or [0])
+        self.lin_width = max([2 * m.heads * m.dim + m.out_width for m in lin] + [m.width for m in gdr] or [0])
         self.state: List[Optional[tuple]] = [None] * len(self.runs)
+        self.canon_ring: List[Optional[tuple]] = [None] * len(self.runs)   # input-convolution rings (mixer, feed-forward) per run
+        self.pool_k: List[Optional[torch.Tensor]] = [None] * len(self.runs)
+        self.pool_v: List[Optional[torch.Tensor]] = [None] * len(self.runs)
         self.num_state_slots = 0
 
     def _alloc_model_buffers(self):
@@ -119,6 +139,9 @@ class LayerListRunner(ModelRunner):
         self.gates = e(T * max(1, self.gate_width), dt=torch.float32)
         self.o_raw = e(T * max(1, self.rec_width), dt=torch.float32)
         self.lin32 = e(T * max(1, self.lin_width), dt=torch.float32)   # prepared q | k | v rows of a linear-attention mixer
+        if self.sandwich:
+            self.y2 = e(T, D, dt=torch.float32)           # the second output of a side-by-side mixer
+            self.h32 = e(T, D, dt=torch.float32)          # a sublayer's normed input before its convolution
         if self.parallel:
             self.y2 = e(T, D, dt=torch.float32)           # the feed-forward's output beside the mixer's (self.y)
             self.emb32 = e(T, D, dt=torch.float32) if self.looped else None   # the embedding output, added again per pass
@@ -148,6 +171,12 @@ class LayerListRunner(ModelRunner):
         self.v_cache = [None] * len(self.runs)
         for l, (li, _) in enumerate(self.runs):          # one cache per RUN of a layer (a repeated span: one per pass)
             m = cfg.layers[li].mixer
+            if m.kind == "side_by_side":
+                m = m.left
+                per_page = m.pool_per_page(self.block_size)
+                # mean key / value of every block of m.pool tokens, fp32, addressed through the KV block table
+                self.pool_k[l] = torch.zeros(num_blocks, m.kv_heads, per_page, m.dim, dtype=torch.float32, device=self.device)
+                self.pool_v[l] = torch.zeros(num_blocks, m.kv_heads, per_page, m.vdim, dtype=torch.float32, device=self.device)
             if m.kind == "attention" and m.kv_from is None:
                 self.k_cache[l] = torch.zeros(num_blocks, m.kv_heads, self.block_size, m.dim, dtype=self.act_dtype,
                                               device=self.device)
@@ -169,9 +198,15 @@ class LayerListRunner(ModelRunner):
         and the stabiliser m [slots, H, Z]."""
         self.num_state_slots = num_slots
         f = lambda *s: torch.zeros(*s, dtype=torch.float32, device=self.device)   # noqa: E731
+        D, R = self.H, self.canon_taps - 1
         for l, (li, _) in enumerate(self.runs):
             m = self.mcfg.layers[li].mixer
-            if m.kind == "linear_attention":         # S [slots, H, dv, dk]
+            if R > 0:        # the last inputs of the mixer's and the feed-forward's convolution, by position mod R
+                self.canon_ring[l] = (f(num_slots, R, D), f(num_slots, R, D) if self.mcfg.layers[li].mlp is not None else None)
+            if m.kind == "side_by_side":             # S [slots, W], and the ring of its convolution's last inputs
+                r = m.right
+                self.state[l] = (f(num_slots, r.width), f(num_slots, r.conv - 1, r.width) if r.conv > 1 else None)
+            if m.kind in ("linear_attention", "gated_linear_attention"):         # S [slots, H, dv, dk]
                 self.state[l] = (f(num_slots, m.heads, m.vdim, m.dim),)
             if m.kind != "mlstm":
                 continue
@@ -192,6 +227,14 @@ class LayerListRunner(ModelRunner):
             ops.streams_step(self.resid32[:T], self.S, hc_read=lw.hc1, norm=(lw.norm1_alpha, lw.norm1, lw.norm1_b),
                              xb_out=self.xb[:T])
             self.stats["kernel_launches"] += 2
+            return
+        if self.sandwich:
+            if self.mcfg.learned_positions:
+                ops.embed_pos(ids, self._pos[:T], self.w.embed, self.w.pos, self.resid32[:T])
+            else:
+                ops.embed_streams(ids, self.w.embed, self.resid32[:T], 1, self.mcfg.embed_scale)
+            self._pending = None
+            self.stats["kernel_launches"] += 1
             return
         if self.parallel:      # the first layer's norm reads the embedding output; a repeated span adds it again
             ops.embed_streams(ids, self.w.embed, self.emb32[:T] if self.looped else self.resid32[:T], 1,
@@ -219,6 +262,34 @@ class LayerListRunner(ModelRunner):
                              x_out=self.resid32[:T])
             self._pending = (None, None)
             self.layer_trace.append(self.resid32[:T].clone())
+
+    def _sandwich_open(self, T: int, pre_w, conv_w, ring, cu_all, ctx_all, slots_all) -> None:
+        """Sandwich residual: the output of the sublayer before (self._pending = (y, y2, ya, yb, post-norm weight))
+        enters the fp32 stream through its norm, the stream is normed for the next sublayer, and the sublayer's input
+        convolution (with the sequences' rings) prepares self.xb."""
+        cfg = self.mcfg
+        y, y2, ya, yb, post_w = self._pending if self._pending is not None else (None, None, 1.0, 1.0, None)
+        h = self.h32[:T] if conv_w is not None else self.xb[:T]
+        ops.sandwich_join(self.resid32[:T], cfg.norm_eps, y=y, y2=y2, ya=ya, yb=yb, post_w=post_w, mult=cfg.residual_mult,
+                          pre_w=pre_w, x_out=self.resid32[:T] if y is not None else None, h_out=h)
+        self._pending = None
+        self.stats["kernel_launches"] += 1
+        if conv_w is not None:
+            ops.causal_conv(h, conv_w, ring, cu_all, ctx_all, slots_all, self.xb[:T], add_input=True)
+            if ring is not None:
+                ops.conv_commit(h, ring, cu_all, ctx_all, slots_all, conv_w.shape[1])
+            self.stats["kernel_launches"] += 2
+
+    def _sandwich_close(self, T: int) -> None:
+        """Materialise the stream after a layer (tracing only: on the serving path the next sublayer's open does it)."""
+        if self.layer_trace is None:
+            return
+        cfg = self.mcfg
+        y, y2, ya, yb, post_w = self._pending
+        ops.sandwich_join(self.resid32[:T], cfg.norm_eps, y=y, y2=y2, ya=ya, yb=yb, post_w=post_w, mult=cfg.residual_mult,
+                          x_out=self.resid32[:T])
+        self._pending = None
+        self.layer_trace.append(self.resid32[:T].clone())
 
     def _join(self, T: int, l: int, q: int) -> None:
         """The branch output self.y of sublayer q (1 mixer, 2 feed-forward) of layer l enters the residual, and the
@@ -283,16 +354,44 @@ class LayerListRunner(ModelRunner):
             out = self._view(self.mix_out, T, m.out_width)
             if self.parallel:
                 self._open_layer(T, l, lw, again)
+            if self.sandwich:
+                ring = self.canon_ring[l] or (None, None)
+                self._sandwich_open(T, lw.norm1, lw.canon1, ring[0], cu_all, ctx_all, slots_all)
             ops.linear(self.xb[:T], lw.proj, proj)
-            if m.kind == "latent_attention":
+            if m.kind == "side_by_side":
+                self._side_by_side(l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d, cu_all, ctx_all,
+                                   slots_all)
+                if layer.mlp is not None:
+                    self._sandwich_open(T, lw.norm2, lw.canon2, ring[1], cu_all, ctx_all, slots_all)
+                    self._feed_forward(T, layer.mlp, lw)
+                    self._pending = (self.y[:T], None, 1.0, 1.0, lw.norm2b)
+                self._sandwich_close(T)
+                continue
+            if m.kind == "gated_linear_attention":
+                H, dk, dv = m.heads, m.dim, m.vdim
+                kc, vc = H * dk, 2 * H * dk
+                gc = vc + H * dv
+                ac = gc + H * dv
+                x32 = self._view(self.lin32, T, gc)
+                # q / sqrt(dk), k, v as fp32 rows; the decay's pre-activation z = A2 (A1 h) + b in fp32
+                ops.rot_prep(proj, 0, kc, vc, pos, None, x32, x32[:, kc:], x32[:, vc:], H, H, dk, dv, paged=False,
+                             q_mul=dk ** -0.5)
+                z = self._view(self.gates, T, kc)
+                ops.linear(proj[:, ac:ac + m.decay_rank], lw.decay_up, z, bias=lw.decay_bias)
+                o_raw = self._view(self.o_raw, T, H * dv)
+                ops.gla_scan(x32, 0, kc, vc, z, 1.0 / m.tau, cu_all, ctx_all, slots_all, self.state[l][0], o_raw, H, dk, dv)
+                ops.linattn_out(o_raw, proj, gc, lw.out_norm, out, H, dv, eps, False, "silu")
+                self.stats["kernel_launches"] += 5
+            elif m.kind == "latent_attention":
                 self._latent_attention(l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d)
             elif m.kind == "attention":
                 own = m.kv_from is None
                 H, G, dk, dv = m.heads, m.kv_heads, m.dim, m.vdim
                 if m.rot is not None or m.values_are_keys or m.qk_unit_norm:
                     # rotation, then the weightless q / k norm; keys to their pages, values = the keys as projected
+                    # (a layer that reads another layer's cache prepares its queries only)
                     ops.rot_prep(proj, 0, H * dk, -1 if m.values_are_keys else (H + G) * dk, pos, slots, proj,
-                                 self.k_cache[l], self.v_cache[l], H, G, dk, dv, paged=True,
+                                 self.k_cache[l] if own else None, self.v_cache[l] if own else None, H, G, dk, dv, paged=True,
                                  rot_dims=m.rot.dims if m.rot is not None else 0,
                                  half_layout=m.rot is not None and m.rot.layout == "half", freq=lw.rot_freq,
                                  unit_norm=m.qk_unit_norm, eps=eps)
@@ -308,7 +407,8 @@ class LayerListRunner(ModelRunner):
                                               window=m.window)
                 elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
-                                          H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window)
+                                          H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window,
+                                          gate_per_head=m.gate_per_head, head_scale=lw.head_scale)
                 if Bd and self.fast_decode[li]:
                     splits, ws = self._decode_plan(Bd, m)
                     ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
@@ -316,7 +416,7 @@ class LayerListRunner(ModelRunner):
                                           gate=proj[Tp:T, gate_col:] if m.gate else None, window=m.window)
                 elif Bd:
                     ops.attn_sink_decode(proj[Tp:T], gate_col, kc, vc, bt_d, lens_d, lw.sink, out[Tp:T], H, G, dk, dv,
-                                         m.scale, window=m.window)
+                                         m.scale, window=m.window, gate_per_head=m.gate_per_head, head_scale=lw.head_scale)
                 self.stats["kernel_launches"] += 2 + (1 if nt else 0) + (1 if Bd else 0)
             elif m.kind == "linear_attention":
                 H, dk, dv = m.heads, m.dim, m.vdim
@@ -343,6 +443,14 @@ class LayerListRunner(ModelRunner):
                 self.stats["kernel_launches"] += 4
             ops.linear(out, lw.o, self.y[:T])
             self.stats["kernel_launches"] += 1
+            if self.sandwich:
+                self._pending = (self.y[:T], None, 1.0, 1.0, lw.norm1b)
+                if layer.mlp is not None:
+                    self._sandwich_open(T, lw.norm2, lw.canon2, ring[1], cu_all, ctx_all, slots_all)
+                    self._feed_forward(T, layer.mlp, lw)
+                    self._pending = (self.y[:T], None, 1.0, 1.0, lw.norm2b)
+                self._sandwich_close(T)
+                continue
             if self.parallel:      # the feed-forward reads the same normed rows; both outputs wait for the next norm
                 if layer.mlp is not None:
                     self._feed_forward(T, layer.mlp, lw, self.y2[:T])
@@ -352,6 +460,52 @@ class LayerListRunner(ModelRunner):
             if layer.mlp is not None:
                 self._feed_forward(T, layer.mlp, lw)
                 self._join(T, li, 2)
+
+    def _side_by_side(self, l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d, cu_all, ctx_all,
+                      slots_all) -> None:
+        """Two mixers on one input.  Left: rotary attention in a sliding window that also sees the mean key / value of
+        every block of tokens wholly before the window (block means kept in a second cache, refreshed for the blocks
+        this step completes).  Right: [y | x] branches -> short convolution of x (ring per sequence) -> block-diagonal
+        gate projections in fp32 -> the gated diagonal recurrence (state slot in / out) times gelu(y).  Each side has
+        its own output projection (fp32); the join that follows mixes them with the mixer's factors."""
+        a, r = m.left, m.right
+        eps = self.mcfg.norm_eps
+        H, G, dk, dv, W = a.heads, a.kv_heads, a.dim, a.vdim, r.width
+        left, right = out[:, :a.out_width], out[:, a.out_width:]
+        kc, vc = self.k_cache[l], self.v_cache[l]
+        ops.rot_prep(proj, 0, H * dk, (H + G) * dk, self._pos, self._slots, proj, kc, vc, H, G, dk, dv, paged=True,
+                     rot_dims=a.rot.dims, half_layout=a.rot.layout == "half", freq=lw.rot_freq, unit_norm=a.qk_unit_norm, eps=eps)
+        pool = None
+        if a.pool:
+            pool = (self.pool_k[l], self.pool_v[l], a.pool)
+            if nt:
+                ops.kv_pool_update(kc, vc, pool[0], pool[1], bt_p, cu_p, ctx_p, cu_p.shape[0] - 1, Tp, a.pool)
+            if Bd:
+                ops.kv_pool_update(kc, vc, pool[0], pool[1], bt_d, None, lens_d, Bd, 1, a.pool)
+        if nt:
+            ops.attn_sink_prefill(proj[:Tp], -1, kc, vc, bt_p, cu_p, ctx_p, ts, tq, None, left[:Tp], H, G, dk, dv, a.scale,
+                                  tile_rows=self.prefill_tile, window=a.window, head_scale=lw.head_scale, pool=pool)
+        if Bd:
+            ops.attn_sink_decode(proj[Tp:T], -1, kc, vc, bt_d, lens_d, None, left[Tp:T], H, G, dk, dv, a.scale,
+                                 window=a.window, head_scale=lw.head_scale, pool=pool)
+        y_col = a.q_width + G * (dk + dv)
+        x_in = proj[:, y_col + W:y_col + 2 * W]
+        S, ring = self.state[l]
+        u = self._view(self.lin32, T, W)
+        ops.causal_conv(x_in, lw.rec_conv, ring, cu_all, ctx_all, slots_all, u, add_input=False, in_bias=lw.rec_bias[W:],
+                        bias=lw.rec_conv_bias)
+        if ring is not None:
+            ops.conv_commit(x_in, ring, cu_all, ctx_all, slots_all, r.conv, in_bias=lw.rec_bias[W:])
+        gates = self._view(self.gates, T, 2 * W)
+        n = W // r.blocks
+        ops.head_linear(u, lw.rec_gates[:r.blocks], gates[:, :W], r.blocks, n=n, k=n, x_head=n, out_head=n)
+        ops.head_linear(u, lw.rec_gates[r.blocks:], gates[:, W:], r.blocks, n=n, k=n, x_head=n, out_head=n)
+        ops.gated_recurrence_scan(u, gates, lw.rec_gate_bias, lw.rec_lam, proj, y_col, lw.rec_bias[:W], cu_all, ctx_all,
+                                  slots_all, S, right, r.gate_c)
+        ops.linear(left, lw.o, self.y[:T])
+        ops.linear(right, lw.o2, self.y2[:T])
+        self._pending = (self.y[:T], self.y2[:T], m.left_scale, m.right_scale, lw.norm1b)
+        self.stats["kernel_launches"] += 9 + (2 if nt else 0) + (2 if Bd else 0)
 
     def _latent_attention(self, l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d) -> None:
         """Latent attention in the absorbed form: scores and values are taken straight from the cached latent rows,
@@ -412,7 +566,7 @@ class LayerListRunner(ModelRunner):
         if mlp.act == "relu2":
             ops.linear(self.xb[:T], lw.up, act, relu2=True)            # squared ReLU in the GEMM's epilogue
         else:
-            ops.gated_linear(self.xb[:T], lw.gate_up, act, mlp.act)
+            ops.gated_linear(self.xb[:T], lw.gate_up, act, mlp.act, mlp.limit)
         ops.linear(act, lw.down, y)
         self.stats["kernel_launches"] += 2
 
@@ -435,7 +589,11 @@ class LayerListRunner(ModelRunner):
         cfg = self.mcfg
         if rows is None:
             rows = self.arange_dev[:n]
-        if self.parallel:      # the last layer's branch outputs enter the sum here, for the wanted rows only
+        if self.sandwich:      # the last sublayer's output enters the sum here, for the wanted rows only
+            y, y2, ya, yb, post_w = self._pending if self._pending is not None else (None, None, 1.0, 1.0, None)
+            ops.sandwich_join(self.resid32, cfg.norm_eps, y=y, y2=y2, ya=ya, yb=yb, post_w=post_w, mult=cfg.residual_mult,
+                              pre_w=self.w.final_norm, rows=rows, h_out=self.x_last[:n])
+        elif self.parallel:      # the last layer's branch outputs enter the sum here, for the wanted rows only
             a, b = self._pending
             ops.add_rms_norm(self.resid32, self.w.final_norm, cfg.norm_eps, a=a, b=b, rows=rows, xb_out=self.x_last[:n])
         elif self.streams:       # sum of the streams, tanh norm

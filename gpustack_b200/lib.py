@@ -131,6 +131,22 @@ SIGNATURES = {
                                            _i64, _vp, _i32, _vp, _vp, _i32, _i64, _vp, _i32, _f32, _i32, _vp]),
     "b200_moe_gather_scaled": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b200_mlstm_out": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
+    "b200_embed_pos_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b200_sandwich_join": (_i32, [_vp, _vp, _vp, _f32, _f32, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp]),
+    "b200_causal_conv": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _i64, _i32, _i32,
+                                _i32, _vp]),
+    "b200_conv_commit": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "b200_kv_pool_update": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                   _i32, _vp]),
+    "b200_attn_sink_prefill_pool": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp,
+                                           _vp, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _i32, _i32, _vp, _vp, _vp,
+                                           _i32, _i32, _vp]),
+    "b200_attn_sink_decode_pool": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
+                                          _i32, _i32, _i32, _f32, _i64, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "b200_gated_recurrence_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32,
+                                          _i32, _f32, _vp]),
+    "b200_gla_scan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
+                             _vp]),
 }
 
 # A process that serves ONE model family may ask for a library linked from that family's sources only

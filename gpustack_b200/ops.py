@@ -528,30 +528,51 @@ def attn_sink_prefill_tile() -> int:
     return load().b200_attn_sink_prefill_tile()
 
 
+def _pool_args(pool, k_cache, dk, dv):
+    """pool = (pool_k, pool_v, block size) or None -> (pool_k ptr, pool_v ptr, block size, entries per page)."""
+    if pool is None:
+        return None, None, 0, 0
+    pk, pv, n = pool
+    _cuda(pk, pv)
+    _req(pk, torch.float32, "pool_k"); _req(pv, torch.float32, "pool_v")
+    per_page = -(-k_cache.shape[2] // n)
+    if pk.shape[2] != per_page or pk.shape[3] != dk or pv.shape[3] != dv:
+        raise B200Error("pooled cache: [blocks, G, ceil(page / pool), width] expected")
+    return _p(pk), _p(pv), int(n), per_page
+
+
 def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out,
-                      H, G, dk, dv, scale, tile_rows: int = 0, v_ld: int = 0, window: int = 0):
+                      H, G, dk, dv, scale, tile_rows: int = 0, v_ld: int = 0, window: int = 0, gate_per_head: bool = False,
+                      head_scale=None, pool=None):
     """v_ld: elements between value rows (0 = dv); v_cache is k_cache and v_ld == dk when the values are the
-    first dv entries of the key rows (a latent cache).  window > 0: position i sees j with 0 <= i - j < window."""
-    _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
+    first dv entries of the key rows (a latent cache).  window > 0: position i sees j with 0 <= i - j < window.
+    gate_per_head: the gate is ONE column per head at gate_col; head_scale: fp32 [H] factors on the score;
+    pool = (pool_k, pool_v, n): beside the window, the mean key / value of every block of n tokens that ends at or
+    before i - window (fp32 caches written by kv_pool_update)."""
+    _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out, head_scale)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_prefill: projection, cache and output must share one element type")
-    check(load().b200_attn_sink_prefill_ex(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
-                                           _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
-                                           _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
-                                           _p(out), out.stride(0), H, G, dk, dv,
-                                           k_cache.shape[2], scale, v_ld, int(window), _stream()), "attn_sink_prefill")
+    pk, pv, pn, ppp = _pool_args(pool, k_cache, dk, dv)
+    check(load().b200_attn_sink_prefill_pool(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                             _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
+                                             _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
+                                             _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, int(window),
+                                             1 if gate_per_head else 0, _p(head_scale), pk, pv, pn, ppp, _stream()),
+          "attn_sink_prefill")
     return out
 
 
 def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale,
-                     v_ld: int = 0, window: int = 0):
-    _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out)
+                     v_ld: int = 0, window: int = 0, gate_per_head: bool = False, head_scale=None, pool=None):
+    _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out, head_scale)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_decode: projection, cache and output must share one element type")
-    check(load().b200_attn_sink_decode_ex(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
-                                          _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
-                                          _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, int(window),
-                                          _stream()), "attn_sink_decode")
+    pk, pv, pn, ppp = _pool_args(pool, k_cache, dk, dv)
+    check(load().b200_attn_sink_decode_pool(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                            _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
+                                            _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, int(window),
+                                            1 if gate_per_head else 0, _p(head_scale), pk, pv, pn, ppp, _stream()),
+          "attn_sink_decode")
     return out
 
 
@@ -603,9 +624,11 @@ def rot_prep(proj, q_col: int, k_col: int, v_col: int, positions, slots, q_out, 
     dst = q_out if q_out is not None else k_out
     if any(t_ is not None and t_.dtype != dst.dtype for t_ in (q_out, k_out, v_out)):
         raise B200Error("rot_prep: one destination element type")
+    if k_out is None:          # a mixer that reads another layer's keys and values: queries only
+        paged, v_out = False, None
     page = k_out.shape[2] if paged else 0
     check(load().b200_rot_prep(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(positions), _p(slots),
-                               _p(q_out), q_out.stride(0), _p(k_out), 0 if paged else k_out.stride(0), _p(v_out),
+                               _p(q_out), q_out.stride(0), _p(k_out), 0 if (paged or k_out is None) else k_out.stride(0), _p(v_out),
                                0 if (paged or v_out is None) else v_out.stride(0), _is_f32(dst), 1 if paged else 0, page,
                                proj.shape[0], H, G, dk, dv, {None: 0, "silu": 1}[feature], rot_dims, 1 if half_layout else 0,
                                _p(freq), 1 if unit_norm else 0, eps, q_mul, k_mul, _stream()), "rot_prep")
@@ -629,6 +652,87 @@ def linattn_out(o_raw, proj, gate_col: int, norm_w, out, H, dv, eps: float, all_
                                   out.stride(0), o_raw.shape[0], H, dv, 1 if all_heads else 0,
                                   {"sigmoid": 0, "silu": 1}[gate_act], eps, _stream()), "linattn_out")
     return out
+
+
+# ------------------------------------------- norm before and after every sublayer, short convolutions, pooled KV blocks
+def embed_pos(ids, positions, table, pos_table, x_out):
+    """x_out[t] (fp32) = table[ids[t]] + pos_table[positions[t]]."""
+    _cuda(ids, positions, table, pos_table, x_out)
+    _req(ids, torch.int32, "ids"); _req(positions, torch.int32, "positions"); _req(table, torch.bfloat16, "table")
+    _req(pos_table, torch.bfloat16, "pos_table"); _req(x_out, torch.float32, "x_out")
+    check(load().b200_embed_pos_f32(_p(ids), _p(positions), _p(table), _p(pos_table), _p(x_out), ids.shape[0], table.shape[1],
+                                    table.shape[0], pos_table.shape[0], _stream()), "embed_pos")
+
+
+def sandwich_join(x_in, eps: float, y=None, y2=None, ya: float = 1.0, yb: float = 1.0, post_w=None, mult: float = 1.0,
+                  pre_w=None, x_out=None, h_out=None, rows=None, zero_centred: bool = True):
+    """z = x_in + mult * norm(ya * y + yb * y2; post_w) (y None: z = x_in); x_out = z; h_out = norm(z; pre_w) in fp32 or
+    bf16.  norm(v; w) = v / sqrt(mean(v^2) + eps) * (1 + w) (zero_centred) or * w.  rows: gather, h_out only."""
+    _cuda(x_in, y, y2, post_w, pre_w, x_out, h_out, rows)
+    for t_, n_ in ((x_in, "x_in"), (y, "y"), (y2, "y2"), (x_out, "x_out")):
+        if t_ is not None:
+            _req(t_, torch.float32, n_)
+    D = x_in.shape[1]
+    T = rows.shape[0] if rows is not None else (h_out if h_out is not None else x_out).shape[0]
+    check(load().b200_sandwich_join(_p(x_in), _p(y), _p(y2), ya, yb, _p(post_w), mult, _p(rows), _p(pre_w), _p(x_out), _p(h_out),
+                                    0 if h_out is None else _is_f32(h_out), T, D, eps, 1 if zero_centred else 0, _stream()),
+          "sandwich_join")
+
+
+def causal_conv(x, w, ring, cu_seq, ctx_lens, state_slots, out, *, add_input: bool, in_bias=None, bias=None):
+    """Causal per-channel convolution over every sequence's new rows (csrc/sandwich.cu).  x [T, C] (a column slice of
+    wider rows is fine), w fp32 [C, taps] (last tap = current token), ring fp32 [slots, taps - 1, C]."""
+    _cuda(x, w, ring, cu_seq, ctx_lens, state_slots, out, in_bias, bias)
+    _req(w, torch.float32, "w")
+    T, Cn = x.shape
+    taps = w.shape[1]
+    if x.stride(1) != 1 or out.stride(1) != 1 or (ring is not None and tuple(ring.shape[1:]) != (taps - 1, Cn)):
+        raise B200Error("causal_conv: contiguous rows and a ring of [slots, taps - 1, channels]")
+    check(load().b200_causal_conv(_p(x), _is_f32(x), x.stride(0), _p(in_bias), _p(w), _p(bias), 1 if add_input else 0, _p(ring),
+                                  _p(cu_seq), _p(ctx_lens), _p(state_slots), state_slots.shape[0], _p(out), _is_f32(out),
+                                  out.stride(0), T, Cn, taps, _stream()), "causal_conv")
+    return out
+
+
+def conv_commit(x, ring, cu_seq, ctx_lens, state_slots, taps: int, in_bias=None):
+    """The last taps - 1 inputs of every sequence's new rows go to its ring; run after causal_conv."""
+    _cuda(x, ring, cu_seq, ctx_lens, state_slots, in_bias)
+    check(load().b200_conv_commit(_p(x), _is_f32(x), x.stride(0), _p(in_bias), _p(ring), _p(cu_seq), _p(ctx_lens),
+                                  _p(state_slots), state_slots.shape[0], x.shape[1], taps, _stream()), "conv_commit")
+
+
+def kv_pool_update(k_cache, v_cache, pool_k, pool_v, block_table, cu_q, ctx_lens, n_seqs: int, max_new: int, pool: int):
+    """Mean key / value of the blocks of `pool` tokens completed by this step's rows.  cu_q None: one new row per
+    sequence, ctx_lens counts it (a decode step's lengths)."""
+    _cuda(k_cache, v_cache, pool_k, pool_v, block_table, cu_q, ctx_lens)
+    _req(pool_k, torch.float32, "pool_k"); _req(pool_v, torch.float32, "pool_v")
+    G, page, dk, dv = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    check(load().b200_kv_pool_update(_p(k_cache), _p(v_cache), _is_f32(k_cache), _p(pool_k), _p(pool_v), _p(block_table),
+                                     block_table.shape[1], _p(cu_q), _p(ctx_lens), n_seqs, max_new, G, dk, dv, page, pool,
+                                     pool_k.shape[2], _stream()), "kv_pool_update")
+
+
+def gated_recurrence_scan(u, gates, gate_bias, lam, proj, y_col: int, y_bias, cu_seq, ctx_lens, state_slots, S, out,
+                          gate_c: float):
+    """Gated diagonal recurrence over every sequence's new rows (csrc/gated_recurrence.cu)."""
+    _cuda(u, gates, gate_bias, lam, proj, y_bias, cu_seq, ctx_lens, state_slots, S, out)
+    for t_, n_ in ((u, "u"), (gates, "gates"), (gate_bias, "gate_bias"), (lam, "lam"), (y_bias, "y_bias"), (S, "S")):
+        _req(t_, torch.float32, n_)
+    W = u.shape[1]
+    if out.dtype != proj.dtype:
+        raise B200Error("gated_recurrence_scan: projection and output share one element type")
+    check(load().b200_gated_recurrence_scan(_p(u), _p(gates), _p(gate_bias), _p(lam), _p(proj), _is_f32(proj), proj.stride(0),
+                                            y_col, _p(y_bias), _p(cu_seq), _p(ctx_lens), _p(state_slots), _p(S), _p(out),
+                                            out.stride(0), state_slots.shape[0], W, gate_c, _stream()), "gated_recurrence_scan")
+    return out
+
+
+def gla_scan(x, q_col: int, k_col: int, v_col: int, z, inv_tau: float, cu_seq, ctx_lens, state_slots, S, o_raw, H, dk, dv):
+    """Linear attention with the decay sigmoid(z)^inv_tau per key channel and token (csrc/gated_linear_attn.cu)."""
+    _cuda(x, z, cu_seq, ctx_lens, state_slots, S, o_raw)
+    _req(x, torch.float32, "x"); _req(z, torch.float32, "z"); _req(S, torch.float32, "S"); _req(o_raw, torch.float32, "o_raw")
+    check(load().b200_gla_scan(_p(x), x.stride(0), q_col, k_col, v_col, _p(z), z.stride(0), inv_tau, _p(cu_seq), _p(ctx_lens),
+                               _p(state_slots), _p(S), _p(o_raw), state_slots.shape[0], H, dk, dv, _stream()), "gla_scan")
 
 
 # ------------------------------------------- residual streams, latent attention, gated / routed feed-forward

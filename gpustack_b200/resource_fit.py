@@ -56,7 +56,14 @@ def _layer_list_workspace(m, e: EngineConfig) -> int:
         x = l.mixer
         if x.kind == "attention":
             kv = 0 if x.kv_from is not None else x.kv_heads * (x.dim + (0 if x.values_are_keys else x.vdim))
-            proj = max(proj, x.q_width + kv + (x.out_width if x.gate else 0))
+            proj = max(proj, x.q_width + kv + x.gate_width + 7)
+        elif x.kind == "side_by_side":
+            y, r = x.left, x.right
+            proj = max(proj, y.q_width + y.kv_heads * (y.dim + y.vdim) + r.proj_rows + 7)
+            gates, lin = max(gates, 2 * r.width), max(lin, r.width)
+        elif x.kind == "gated_linear_attention":
+            proj = max(proj, x.proj_rows + 7)
+            gates, rec, lin = max(gates, x.heads * x.dim), max(rec, x.out_width), max(lin, 2 * x.heads * x.dim + x.out_width)
         elif x.kind == "linear_attention":
             proj = max(proj, x.proj_rows)
             rec, lin = max(rec, x.out_width), max(lin, 2 * x.heads * x.dim + x.out_width)
@@ -76,6 +83,8 @@ def _layer_list_workspace(m, e: EngineConfig) -> int:
             ff = max(ff, l.mlp.ff)
     S_smp = min(T, max(S, e.max_logit_rows or 0))
     par = 4 * (1 + (1 if m.loop_times > 1 else 0)) if m.residual == "parallel" else 0    # second branch output, embedding copy
+    if m.residual == "sandwich":
+        par = 8                                                                          # second output, normed input (fp32)
     act = T * (D * (4 * getattr(m, "n_streams", 1) + a + 4 + par) + (proj + mix + ff + lat) * a + (gates + rec + lin) * 4) + routed
     max_len = e.max_model_len or m.max_position_embeddings
     staging = (3 * T + 10 * S + 3 * S_smp + S * math.ceil(max_len / e.block_size) + 2 * T) * 4

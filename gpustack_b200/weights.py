@@ -378,6 +378,25 @@ class LayerListLayer:
     w2: Optional[torch.Tensor] = None            # [experts * D, ff]
     shared13: Optional[torch.Tensor] = None      # [2 shared_ff, D]
     shared2: Optional[torch.Tensor] = None       # [D, shared_ff]
+    # sandwich residual: the norms after the mixer and after the feed-forward
+    norm1b: Optional[torch.Tensor] = None
+    norm2b: Optional[torch.Tensor] = None
+    # input convolution of the mixer / the feed-forward: fp32 [D, taps]
+    canon1: Optional[torch.Tensor] = None
+    canon2: Optional[torch.Tensor] = None
+    head_scale: Optional[torch.Tensor] = None    # attention: fp32 [H], a factor per head on the score
+    # side-by-side mixer: proj rows = [q | k | v (left attention) | y | x (recurrent branch)], zero rows up to a multiple
+    # of 8; `o` is the left output projection, `o2` the right one
+    o2: Optional[torch.Tensor] = None
+    rec_bias: Optional[torch.Tensor] = None      # fp32 [2 W]: biases of the y and x rows
+    rec_conv: Optional[torch.Tensor] = None      # fp32 [W, taps]
+    rec_conv_bias: Optional[torch.Tensor] = None  # fp32 [W]
+    rec_gates: Optional[torch.Tensor] = None     # bf16 [2 * blocks, n, n]: the recurrence gate's blocks, then the input gate's
+    rec_gate_bias: Optional[torch.Tensor] = None  # fp32 [2 W]
+    rec_lam: Optional[torch.Tensor] = None       # fp32 [W]
+    # gated linear attention: proj rows = [q | k | v | gate | decay latent]; the decay's second projection and bias
+    decay_up: Optional[torch.Tensor] = None      # bf16 [H*dk, rank]
+    decay_bias: Optional[torch.Tensor] = None    # bf16 [H*dk]
 
 
 @dataclass
@@ -390,6 +409,7 @@ class LayerListWeights:
     vocab_end: int = 0
     final_norm_b: Optional[torch.Tensor] = None
     final_norm_alpha: Optional[torch.Tensor] = None
+    pos: Optional[torch.Tensor] = None           # learned positions [max_position_embeddings, D]
 
 
 def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
@@ -408,9 +428,54 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
 
     if tanh:
         norm_shapes("final.norm")
+    sandwich = getattr(cfg, "residual", "post_ln") == "sandwich"
+    taps = getattr(cfg, "canon_taps", 0)
+    if getattr(cfg, "learned_positions", False):
+        shapes["pos"] = (cfg.max_position_embeddings, D)
+
+    def attention_shapes(q, m):
+        shapes[q + "q"] = (m.q_width, D)
+        if m.kv_from is None:
+            shapes[q + "k"], shapes[q + "v"] = (m.kv_heads * m.dim, D), (m.kv_heads * m.vdim, D)
+        if m.gate:
+            shapes[q + "g"] = (m.gate_width, D)
+        if m.head_temp:
+            shapes[q + "temp"] = (m.heads,)
+        shapes[q + "o"] = (D, m.out_width)
+
     for l, layer in enumerate(cfg.layers):
         p, m = f"l{l}.", layer.mixer
         norm_shapes(p + "norm1")
+        if sandwich:
+            shapes[p + "norm1b"] = (D,)
+            if taps:
+                shapes[p + "canon1"] = (D, taps)
+            if m.kind == "attention":
+                attention_shapes(p + "mix.", m)
+            elif m.kind == "side_by_side":
+                attention_shapes(p + "mix.left.", m.left)
+                r, q = m.right, p + "mix.right."
+                n = r.width // r.blocks
+                for b_ in ("y", "x"):
+                    shapes[q + b_], shapes[q + b_ + ".b"] = (r.width, D), (r.width,)
+                shapes[q + "conv"], shapes[q + "conv.b"] = (r.width, r.conv), (r.width,)
+                for g_ in ("ra", "ri"):
+                    shapes[q + g_], shapes[q + g_ + ".b"] = (r.blocks, n, n), (r.blocks, n)
+                shapes[q + "lam"], shapes[q + "o"] = (r.width,), (D, r.width)
+            else:
+                q = p + "mix."
+                shapes[q + "q"] = shapes[q + "k"] = (m.heads * m.dim, D)
+                shapes[q + "v"] = shapes[q + "g"] = (m.out_width, D)
+                shapes[q + "o"], shapes[q + "norm"] = (D, m.out_width), (m.vdim,)
+                shapes[q + "a1"], shapes[q + "a2"], shapes[q + "a2.b"] = (m.decay_rank, D), (m.heads * m.dim, m.decay_rank), \
+                    (m.heads * m.dim,)
+            if layer.mlp is not None:
+                shapes[p + "norm2"] = shapes[p + "norm2b"] = (D,)
+                if taps:
+                    shapes[p + "canon2"] = (D, taps)
+                shapes[p + "mlp.gate"] = shapes[p + "mlp.up"] = (layer.mlp.ff, D)
+                shapes[p + "mlp.down"] = (D, layer.mlp.ff)
+            continue
         for q in ((1, 2) if layer.mlp is not None else (1,)) if S else ():
             shapes[p + f"hc{q}.in"], shapes[p + f"hc{q}.out"], shapes[p + f"hc{q}.mix"] = (S,), (S,), (S, S)
         if m.kind == "latent_attention":
@@ -512,9 +577,54 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
             return torch.ones(3, dtype=torch.float32, device=device)
         return torch.cat([f32(prefix + ".in"), f32(prefix + ".out"), f32(prefix + ".mix")]).contiguous()
 
+    def cat8(names):
+        """Fused projection rows, zero rows up to a multiple of 8 (16-byte output rows for the tensor-core GEMM)."""
+        w = cat(names)
+        pad = -w.shape[0] % 8
+        return w if not pad else torch.cat([w, torch.zeros(pad, w.shape[1], dtype=BF16, device=device)]).contiguous()
+
+    def freq_of(rot):
+        return torch.tensor(list(rot.frequencies()[0]), dtype=torch.float64).to(device)
+
     layers = []
     for l, layer in enumerate(cfg.layers):
         p, m = f"l{l}.", layer.mixer
+        if getattr(cfg, "residual", "post_ln") == "sandwich":
+            q = p + "mix."
+            if m.kind == "attention":
+                own = m.kv_from is None
+                lw = LayerListLayer(norm1=g(p + "norm1"), o=g(q + "o"),
+                                    proj=cat8([q + n for n in ["q"] + (["k", "v"] if own else []) + (["g"] if m.gate else [])]))
+                lw.rot_freq = freq_of(m.rot)
+            elif m.kind == "side_by_side":
+                a, r = m.left, m.right
+                lw = LayerListLayer(norm1=g(p + "norm1"), o=g(q + "left.o"), o2=g(q + "right.o"),
+                                    proj=cat8([q + "left.q", q + "left.k", q + "left.v", q + "right.y", q + "right.x"]))
+                lw.rot_freq = freq_of(a.rot)
+                lw.head_scale = f32(q + "left.temp") if a.head_temp else None
+                lw.rec_bias = torch.cat([f32(q + "right.y.b"), f32(q + "right.x.b")]).contiguous()
+                lw.rec_conv = g(q + "right.conv").to(torch.float32).contiguous()
+                lw.rec_conv_bias = f32(q + "right.conv.b")
+                lw.rec_gates = torch.cat([g(q + "right.ra"), g(q + "right.ri")], dim=0).contiguous()
+                lw.rec_gate_bias = torch.cat([f32(q + "right.ra.b"), f32(q + "right.ri.b")]).contiguous()
+                lw.rec_lam = f32(q + "right.lam")
+            else:
+                a1 = get(q + "a1")
+                m.decay_rank = int(a1.shape[0])          # the checkpoint decides the rank of the decay's latent
+                shapes.update(layer_list_tensor_shapes(cfg))
+                lw = LayerListLayer(norm1=g(p + "norm1"), o=g(q + "o"), out_norm=g(q + "norm"),
+                                    proj=cat8([q + n for n in ("q", "k", "v", "g", "a1")]))
+                lw.decay_up, lw.decay_bias = g(q + "a2"), g(q + "a2.b")
+            lw.norm1b = g(p + "norm1b")
+            if getattr(cfg, "canon_taps", 0):
+                lw.canon1 = g(p + "canon1").to(torch.float32).contiguous()
+            if layer.mlp is not None:
+                lw.norm2, lw.norm2b = g(p + "norm2"), g(p + "norm2b")
+                if getattr(cfg, "canon_taps", 0):
+                    lw.canon2 = g(p + "canon2").to(torch.float32).contiguous()
+                lw.gate_up, lw.down = _interleave_rows(g(p + "mlp.gate"), g(p + "mlp.up")), g(p + "mlp.down")
+            layers.append(lw)
+            continue
         if m.kind == "latent_attention":
             first = g(p + "mix.dq") if m.q_rank else g(p + "mix.q")
             lw = LayerListLayer(norm1=g(p + "norm1"), proj=torch.cat([first, g(p + "mix.dkv")], dim=0).contiguous(),
@@ -585,6 +695,8 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
                            vocab_start=0, vocab_end=cfg.vocab_size)
     if tanh:
         out.final_norm_b, out.final_norm_alpha = g("final.norm.b"), f32("final.norm.alpha")
+    if getattr(cfg, "learned_positions", False):
+        out.pos = g("pos")
     return out
 
 
@@ -621,6 +733,23 @@ def random_layer_list_state(cfg, seed: int = 0, device: str = "cpu") -> Dict[str
             x = 0.7 + 0.2 * x
         elif leaf == "mlp.correction":
             x = 0.05 * x
+        elif getattr(cfg, "norm", "") == "rms_zero_centred" and (leaf.endswith("norm") or leaf[:5] in ("norm1", "norm2")) \
+                and leaf != "mix.norm":
+            x = 0.2 * x                                   # stored around zero
+        elif leaf == "pos":
+            x = 0.5 * x
+        elif leaf in ("canon1", "canon2"):
+            x = 0.4 * x
+        elif leaf.endswith(".temp"):
+            x = 1.0 + 0.3 * x
+        elif leaf.endswith(".lam"):
+            x = -1.0 + x                                  # decays spread between fast and slow
+        elif leaf.endswith(".conv"):
+            x = 0.5 * x
+        elif leaf.endswith(".ra") or leaf.endswith(".ri"):
+            x = x / (shape[-1] ** 0.5)
+        elif leaf == "mix.a2.b":
+            x = 2.0 + x                                   # sigmoid(z) mostly near one: a long memory
         elif leaf.endswith("norm") or leaf in ("norm1", "norm2"):
             x = 1.0 + 0.2 * x
         elif leaf == "mix.f.b":

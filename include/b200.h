@@ -432,6 +432,52 @@ int b200_linear_simt_grouped_ex(const void* X, int x_f32, const void* W, void* Y
 int b200_moe_gather_scaled(const void* x, const int32_t* row_pair, const int32_t* num_tiles, void* xp, int H, int K,
                            int capacity_rows, const float* row_scale, void* stream);
 
+/* ---- residual stream with a norm before and after every sublayer; short causal convolutions; pooled KV blocks ---- */
+/* x[t] = table[ids[t]] + pos_table[positions[t]] (fp32). */
+int b200_embed_pos_f32(const int32_t* ids, const int32_t* positions, const void* table, const void* pos_table, float* x,
+                       int T, int D, int vocab, int max_pos, void* stream);
+/* v = ya*y (+ yb*y2); z = x_in + mult * v / rms(v) * wb (y == NULL: z = x_in); x_out = z; h_out = z / rms(z) * wa.
+ * zero_centred: the stored weights enter as 1 + w.  rows: gather (h_out only). */
+int b200_sandwich_join(const float* x_in, const float* y, const float* y2, float ya, float yb, const void* wb, float mult,
+                       const int32_t* rows, const void* wa, float* x_out, void* h_out, int h_f32, int T, int D, float eps,
+                       int zero_centred, void* stream);
+/* out_t = (in_t if add_input) + bias + sum_j w[c][j] in_(t - taps + 1 + j) over every sequence's new rows; older inputs
+ * come from ring [slots][taps - 1][C] (entry = position mod (taps - 1)); in_bias is added to every input. */
+int b200_causal_conv(const void* in, int in_f32, int64_t ld_in, const float* in_bias, const float* w, const float* bias,
+                     int add_input, const float* ring, const int32_t* cu_seq, const int32_t* ctx_lens,
+                     const int32_t* state_slots, int n_seqs, void* out, int out_f32, int64_t ld_out, int T, int C, int taps,
+                     void* stream);
+/* The last taps - 1 inputs of every sequence's new rows go to its ring (run after b200_causal_conv). */
+int b200_conv_commit(const void* in, int in_f32, int64_t ld_in, const float* in_bias, float* ring, const int32_t* cu_seq,
+                     const int32_t* ctx_lens, const int32_t* state_slots, int n_seqs, int C, int taps, void* stream);
+/* Mean key / value (fp32) of every block of `pool` tokens that this step completes.  cu_q == NULL: one new row per
+ * sequence and ctx_lens counts it. */
+int b200_kv_pool_update(const void* k_cache, const void* v_cache, int f32, float* pool_k, float* pool_v,
+                        const int32_t* block_table, int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens, int n_seqs,
+                        int max_new, int G, int dk, int dv, int page, int pool, int per_page, void* stream);
+/* b200_attn_sink_prefill_ex / _decode_ex with a gate of one number per head, a score factor per head and pooled blocks. */
+int b200_attn_sink_prefill_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache, const void* v_cache,
+                                const int32_t* block_table, int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink,
+                                void* out, int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                int window, int gate_per_head, const float* head_scale, const float* pool_k,
+                                const float* pool_v, int pool, int per_page, void* stream);
+int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache, const void* v_cache,
+                               const int32_t* block_table, int max_blocks, const int32_t* seq_lens, int B, const float* sink,
+                               void* out, int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                               int window, int gate_per_head, const float* head_scale, const float* pool_k,
+                               const float* pool_v, int pool, int per_page, void* stream);
+/* Gated diagonal recurrence over every sequence's new rows: u [T][W], gates [T][2W] (recurrence | input gate
+ * pre-activations), S [slots][W]; out = S_t * gelu_tanh(proj[t][y_col + c] + y_bias[c]). */
+int b200_gated_recurrence_scan(const float* u, const float* gates, const float* gate_bias, const float* lam, const void* proj,
+                               int f32, int64_t ld, int y_col, const float* y_bias, const int32_t* cu_seq,
+                               const int32_t* ctx_lens, const int32_t* state_slots, float* S, void* out, int64_t ldo,
+                               int n_seqs, int W, float gate_c, void* stream);
+/* Linear attention with a decay per key channel and token, alpha = sigmoid(z)^inv_tau: S [slots][H][dv][dk]. */
+int b200_gla_scan(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* z, int64_t ldz, float inv_tau,
+                  const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S, float* o_raw,
+                  int n_seqs, int H, int dk, int dv, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
