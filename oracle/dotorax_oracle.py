@@ -103,8 +103,8 @@ def pooled_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     G = k.shape[1]
     out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
     nb_all = T // pool
-    kb = k[:nb_all * pool].reshape(nb_all, pool, G, -1).mean(dim=1)
-    vb = v[:nb_all * pool].reshape(nb_all, pool, G, -1).mean(dim=1)
+    kb = k[:nb_all * pool].reshape(nb_all, pool, G, k.shape[2]).mean(dim=1)
+    vb = v[:nb_all * pool].reshape(nb_all, pool, G, v.shape[2]).mean(dim=1)
     for h in range(H):
         g = h // (H // G)
         for i in range(T):
@@ -243,3 +243,88 @@ def forward(cfg: dict, state: Dict[str, torch.Tensor], tokens: List[int], dtype=
         if trace is not None:
             trace.append(x.clone())
     return zero_centred_rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+# ------------------------------------------------------------------------------ random models (tests)
+def tensor_shapes(cfg: dict, decay_rank: int = 6) -> Dict[str, tuple]:
+    """Tensor names and shapes of a checkpoint of this design; decay_rank: the rank of a gla mixer's decay projection
+    (a checkpoint property: the configuration does not give it)."""
+    D = int(cfg["width"])
+    taps = int(cfg["canon"]["taps"])
+    out: Dict[str, tuple] = {"embed": (int(cfg["vocab"]), D), "pos": (int(cfg["max_positions"]), D), "final.norm": (D,),
+                             "head": (int(cfg["vocab"]), D)}
+
+    def attention(p, mx, gate):
+        H, G, dk, dv = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"]), int(mx["vdim"])
+        out[p + "q"] = (H * dk, D)
+        if mx.get("kv_from") is None:
+            out[p + "k"], out[p + "v"] = (G * dk, D), (G * dv, D)
+        if gate:
+            out[p + "g"] = (H, D)
+        else:
+            out[p + "temp"] = (H,)
+        out[p + "o"] = (D, H * dv)
+
+    for l, layer in enumerate(cfg["layers"]):
+        p, mx = f"l{l}.", layer["mixer"]
+        out[p + "norm1"] = out[p + "norm1b"] = (D,)
+        out[p + "canon1"] = (D, taps)
+        if layer["type"] == "attention":
+            attention(p + "mix.", mx, True)
+        elif layer["type"] == "parallel":
+            attention(p + "mix.left.", mx["left"], False)
+            R = mx["right"]
+            W, B = int(R["width"]), int(R["blocks"])
+            q = p + "mix.right."
+            out[q + "y"] = out[q + "x"] = (W, D)
+            out[q + "y.b"] = out[q + "x.b"] = out[q + "conv.b"] = out[q + "lam"] = (W,)
+            out[q + "conv"] = (W, int(R["conv"]))
+            out[q + "ra"] = out[q + "ri"] = (B, W // B, W // B)
+            out[q + "ra.b"] = out[q + "ri.b"] = (B, W // B)
+            out[q + "o"] = (D, W)
+        else:
+            H, dk, dv = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
+            q = p + "mix."
+            out[q + "q"] = out[q + "k"] = (H * dk, D)
+            out[q + "v"] = out[q + "g"] = (H * dv, D)
+            out[q + "o"], out[q + "norm"] = (D, H * dv), (dv,)
+            out[q + "a1"], out[q + "a2"], out[q + "a2.b"] = (decay_rank, D), (H * dk, decay_rank), (H * dk,)
+        if layer.get("mlp") is not None:
+            ff = int(layer["mlp"]["ff"])
+            out[p + "norm2"] = out[p + "norm2b"] = (D,)
+            out[p + "canon2"] = (D, taps)
+            out[p + "mlp.gate"] = out[p + "mlp.up"] = (ff, D)
+            out[p + "mlp.down"] = (D, ff)
+    return out
+
+
+def random_weights(cfg: dict, seed: int = 0, decay_rank: int = 6) -> Dict[str, torch.Tensor]:
+    """Seeded bf16 weights: linear weights N(0, 1 / in); norm weights around zero (the design stores them so) except the
+    gla output norm around one; decays spread from fast to slow."""
+    g = torch.Generator().manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in tensor_shapes(cfg, decay_rank).items():
+        x = torch.randn(tuple(shape), generator=g)
+        leaf = name.split(".")[-1]
+        if name.endswith("mix.norm"):
+            x = 1.0 + 0.2 * x
+        elif leaf.startswith("norm"):
+            x = 0.25 * x
+        elif leaf == "pos":
+            x = 0.5 * x
+        elif leaf in ("canon1", "canon2", "conv"):
+            x = 0.5 * x
+        elif leaf == "temp":
+            x = 1.0 + 0.3 * x
+        elif leaf == "lam":
+            x = 1.5 * x - 1.0
+        elif name.endswith("a2.b"):
+            x = 2.0 + 1.5 * x
+        elif name.endswith("a2"):
+            x = 2.0 * x / math.sqrt(shape[-1])
+        elif leaf == "b":
+            x = 0.3 * x
+        elif name != "embed":
+            x = x / math.sqrt(shape[-1])
+        out[name] = x.to(torch.bfloat16)
+    return out
