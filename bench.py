@@ -67,7 +67,7 @@ def parse_args():
     ap.add_argument("--cpu-sample-output", type=int, default=16)
     ap.add_argument("--no-cpu-configs0", action="store_true",
                     help="skip the BASELINE configs[0] CPU leg (Qwen2-0.5B shape, 32 requests on the host cores)")
-    ap.add_argument("--family", default=None, choices=[None, "vodavik", "danipel", "resevik"],
+    ap.add_argument("--family", default=None, choices=[None, "vodavik", "danipel", "resevik", "dotorax"],
                     help="side benchmark of another model family beside the closest Llama-class model of equal layer "
                          "sizes (prefill / decode tokens per second and per-kernel roofline fractions); prints its own "
                          "JSON line and leaves the default workload alone")

@@ -249,8 +249,7 @@ class AttentionSpec:
     def tile_sized(self) -> bool:
         """Keys and values share one width that is a tensor-core tile (64 / 128) and the group fits the decode
         kernel: the Llama-class attention kernels (with sink and gate) can serve this mixer in bf16."""
-        return (self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
-                and not self.pool and not (self.gate and self.gate_per_head))
+        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16 and not self.pool
 
     @property
     def gate_width(self) -> int:

@@ -62,11 +62,11 @@ __device__ __forceinline__ void load_page(uint8_t* dst, const bf16* __restrict__
 // being kept in the base-2 domain) and a sigmoid output gate read from gate[b][h*D + d].
 __device__ __forceinline__ bf16 finish_row(float num, float den, float mm, const float* __restrict__ sink,
                                            const bf16* __restrict__ gate, int64_t gate_stride, int b, int h, int D,
-                                           int d) {
+                                           int d, int gate_per_head = 0) {
   if (sink != nullptr && mm > -INFINITY) den += exp2f(sink[h] * 1.4426950408889634f - mm);
   float o = den > 0.f ? num / den : 0.f;
   if (gate != nullptr) {
-    const float gv = __bfloat162float(gate[(size_t)b * gate_stride + (size_t)h * D + d]);
+    const float gv = __bfloat162float(gate[(size_t)b * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * D + d)]);
     o *= 1.f / (1.f + __expf(-gv));
   }
   return __float2bfloat16_rn(o);
@@ -81,7 +81,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
                          float* __restrict__ ws_o, float* __restrict__ ws_ml, int num_splits,
                          int Hq, int Hkv, float scale_log2, uint32_t* __restrict__ split_ctr,
                          const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride,
-                         int window) {
+                         int window, int gate_per_head) {
   pdl_launch_dependents();
   pdl_wait();
   using Cfg = DecCfg<D>;
@@ -264,7 +264,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
     }
     const int h = kvh * G + g;
     if (num_splits == 1) {
-      out[((size_t)b * Hq + h) * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, h, D, d);
+      out[((size_t)b * Hq + h) * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, h, D, d, gate_per_head);
     } else {
       const size_t slot = ((size_t)b * Hq + h) * num_splits + split;
       ws_o[slot * D + d] = num;
@@ -301,7 +301,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
       den += sc * __ldcg(ml + sp * 2 + 1);
       num += sc * __ldcg(ws_o + (row * num_splits + sp) * D + d);
     }
-    out[row * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, kvh * G + g, D, d);
+    out[row * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, kvh * G + g, D, d, gate_per_head);
   }
 }
 
@@ -740,6 +740,17 @@ extern "C" int b200_paged_attn_decode_win(const void* q, int64_t q_stride, const
                                           void* workspace, int num_splits, int B, int Hq, int Hkv,
                                           int D, int block_size, float scale, const float* sink,
                                           const void* gate, int64_t gate_stride, int window, void* stream) {
+  return b200_paged_attn_decode_hg(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_lens, out, workspace, num_splits,
+                                   B, Hq, Hkv, D, block_size, scale, sink, gate, gate_stride, window, 0, stream);
+}
+
+extern "C" int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const void* k_cache,
+                                         const void* v_cache, const int32_t* block_table,
+                                         int max_blocks, const int32_t* seq_lens, void* out,
+                                         void* workspace, int num_splits, int B, int Hq, int Hkv,
+                                         int D, int block_size, float scale, const float* sink,
+                                         const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                                         void* stream) {
   B200_REQUIRE(window >= 0, "attn_decode: window %d", window);
   B200_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attn_decode: bad head counts");
   B200_REQUIRE(Hq / Hkv <= 16, "attn_decode: group size %d > 16 unsupported", Hq / Hkv);
@@ -768,7 +779,7 @@ extern "C" int b200_paged_attn_decode_win(const void* q, int64_t q_stride, const
     (void)launch_pdl(paged_attn_decode_kernel<128>, dim3(grid), dim3(kDecWarps * 32), DecCfg<128>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride, window);
+        (const bf16*)gate, gate_stride, window, gate_per_head);
     rc = b200_check_launch("b200_paged_attn_decode");
   } else {
     static bool once = false;
@@ -780,7 +791,7 @@ extern "C" int b200_paged_attn_decode_win(const void* q, int64_t q_stride, const
     (void)launch_pdl(paged_attn_decode_kernel<64>, dim3(grid), dim3(kDecWarps * 32), DecCfg<64>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride, window);
+        (const bf16*)gate, gate_stride, window, gate_per_head);
     rc = b200_check_launch("b200_paged_attn_decode");
   }
   return rc;
@@ -801,7 +812,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
                           void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream,
                           const float* sink = nullptr, const void* gate = nullptr, int64_t gate_stride = 0,
-                          int window = 0);
+                          int window = 0, int gate_per_head = 0, float* lse_out = nullptr);
 }  // namespace b200
 
 extern "C" int b200_attn_prefill_tc_covers(int Hq, int Hkv, int D) {
@@ -827,13 +838,37 @@ extern "C" int b200_paged_attn_prefill_win(const void* q, int64_t q_stride, int 
                                            const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
                                            int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
                                            const void* gate, int64_t gate_stride, int window, void* stream) {
+  return b200_paged_attn_prefill_hg(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,
+                                    ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, block_size, scale, sink, gate,
+                                    gate_stride, window, 0, stream);
+}
+
+extern "C" int b200_paged_attn_prefill_hg(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
+                                          const void* v_cache, int num_blocks, const int32_t* block_table,
+                                          int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                          const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
+                                          int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                          const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                                          void* stream) {
+  return b200_paged_attn_prefill_lse(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,
+                                     ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, block_size, scale, sink, gate,
+                                     gate_stride, window, gate_per_head, nullptr, stream);
+}
+
+extern "C" int b200_paged_attn_prefill_lse(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
+                                           const void* v_cache, int num_blocks, const int32_t* block_table,
+                                           int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                           const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
+                                           int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                           const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                                           float* lse_out, void* stream) {
   B200_REQUIRE(window >= 0, "attn_prefill_ex: window %d", window);
   B200_REQUIRE(b200_attn_prefill_tc_covers(Hq, Hkv, D), "attn_prefill_ex: heads %d / %d x %d not covered", Hq, Hkv, D);
   B200_REQUIRE(block_size == kPage, "attn_prefill_ex: block_size must be %d", kPage);
   if (num_tiles <= 0) return B200_OK;
   const int rc = paged_attn_prefill_tc(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks,
                                        cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, scale,
-                                       (cudaStream_t)stream, sink, gate, gate_stride, window);
+                                       (cudaStream_t)stream, sink, gate, gate_stride, window, gate_per_head, lse_out);
   if (rc > 0) {
     b200_set_error("attn_prefill_ex: the tensor-core kernel does not take this call (alignment or device)");
     return B200_ERR_UNSUPPORTED;

@@ -76,7 +76,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                              const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                              int num_tiles, bf16* __restrict__ out, int Hq, int Hkv, float scale_log2,
                              const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride,
-                             int window) {
+                             int window, int gate_per_head, float* __restrict__ lse_out) {
   constexpr int TPT = 128 / G;   // query tokens per tile
   extern __shared__ uint8_t fa_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) &
@@ -405,12 +405,21 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // softmax sink (mixers that have one): a learned per-head logit that joins the denominator only;
       // l is relative to the reference maximum m_used of the base-2 domain
       if (sink != nullptr && m_used > -INFINITY) l += exp2f(sink[m.kvh * G + g] * 1.4426950408889634f - m_used);
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      // the row's log-sum-exp (natural logarithm of the softmax denominator), for a caller that goes on with more keys
+      if (lse_out != nullptr && valid)
+        lse_out[(size_t)(m.q_begin + qi) * Hq + (size_t)(m.kvh * G + g)] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       bf16* orow = out + ((size_t)(m.q_begin + qi) * Hq + (size_t)(m.kvh * G + g)) * kFaD;
-      // sigmoid output gate (mixers that have one): gate[token][head * D + column], same columns as the row
-      const bf16* grow = (gate != nullptr && valid)
+      // sigmoid output gate (mixers that have one): gate[token][head * D + column], same columns as the row -- or ONE
+      // number per head, gate[token][head], which joins the row's normaliser
+      const bf16* grow = (gate != nullptr && valid && !gate_per_head)
                              ? gate + (size_t)(m.q_begin + qi) * gate_stride + (size_t)(m.kvh * G + g) * kFaD
                              : nullptr;
+      if (gate != nullptr && valid && gate_per_head) {
+        const float gv = __bfloat162float(gate[(size_t)(m.q_begin + qi) * gate_stride + (size_t)(m.kvh * G + g)]);
+        inv *= 1.f / (1.f + __expf(-gv));
+      }
       auto store32 = [&](const uint32_t (&o)[32], bf16* dst) {            // 32 fp32 columns -> 64 bytes of the row
         uint4 wv[4];
         float f[32];
@@ -477,7 +486,8 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
                              const void* v_cache, int num_blocks, const int32_t* block_table, int max_blocks,
                              const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                              const int32_t* tile_q0, int num_tiles, void* out, int Hq, int Hkv, float scale,
-                             const float* sink, const void* gate, int64_t gate_stride, int window, cudaStream_t stream) {
+                             const float* sink, const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                             float* lse_out, cudaStream_t stream) {
   auto kernel = paged_attn_prefill_tc_kernel<G, P_TMEM>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -509,7 +519,7 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
   const int grid = (int)(persist ? (total_work < 2LL * sms ? total_work : 2LL * sms) : total_work);
   cudaError_t e = launch_pdl(kernel, dim3(grid), dim3(kFaThreads), (size_t)kFaSmemBytes, stream, 1, tq, tk, tv,
                              block_table, max_blocks, cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, (bf16*)out, Hq,
-                             Hkv, scale_log2, sink, (const bf16*)gate, gate_stride, window);
+                             Hkv, scale_log2, sink, (const bf16*)gate, gate_stride, window, gate_per_head, lse_out);
   if (e != cudaSuccess) {
     b200_set_error("b200_paged_attn_prefill(tc): launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
@@ -524,7 +534,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
                           int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
                           void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream, const float* sink,
-                          const void* gate, int64_t gate_stride, int window) {
+                          const void* gate, int64_t gate_stride, int window, int gate_per_head, float* lse_out) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("B200_ATTN_PREFILL_TC");   // =0: keep the mma.sync kernels (A/B runs)
@@ -534,7 +544,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
   const DeviceInfo& d = device_info();
   if (!enabled || D != kFaD || (G != 4 && G != 8) || !d.valid || d.cc_major != 10) return 1;
   if (num_tokens <= 0 || num_blocks <= 0 || (q_stride % 8) != 0) return 1;
-  if (gate != nullptr && ((gate_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(gate) & 15))) return 1;
+  if (gate != nullptr && !gate_per_head && ((gate_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(gate) & 15))) return 1;
   static int p_tmem = -1;
   if (p_tmem < 0) {
     const char* e = getenv("B200_ATTN_P_TMEM");   // =0: P through shared memory (A/B runs)
@@ -542,7 +552,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
   }
 #define B200_FA_LAUNCH(GG, PT)                                                                                       \
   launch_prefill_tc<GG, PT>(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,    \
-                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, sink, gate, gate_stride, window, stream)
+                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, sink, gate, gate_stride, window, gate_per_head, lse_out, stream)
   if (G == 4) return p_tmem ? B200_FA_LAUNCH(4, true) : B200_FA_LAUNCH(4, false);
   return p_tmem ? B200_FA_LAUNCH(8, true) : B200_FA_LAUNCH(8, false);
 #undef B200_FA_LAUNCH

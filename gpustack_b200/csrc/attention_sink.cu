@@ -198,7 +198,8 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
                          const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                          const float* __restrict__ sink, TA* out, int64_t ldo, int H, int G, int dk, int dv, int page,
                          float scale, int64_t v_ld, int window, int gate_per_head, const float* __restrict__ head_scale,
-                         const float* __restrict__ pool_k, const float* __restrict__ pool_v, int pool, int per_page) {
+                         const float* __restrict__ pool_k, const float* __restrict__ pool_v, int pool, int per_page,
+                         const float* __restrict__ init_lse) {
   extern __shared__ float smem[];
   float* Qs = smem;                                   // [16][dk]
   float* Ks = Qs + kPfRows * dk;                      // [32][dk + 1]
@@ -226,6 +227,23 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
 #pragma unroll
     for (int j = 0; j < kMaxDvPerLane; ++j) acc[r][j] = 0.f;
   }
+  if (init_lse != nullptr) {
+    // the softmax is CONTINUED: another kernel has attended the window's tokens, `out` holds its normalised rows and
+    // init_lse their log-sum-exp -- a running state with maximum lse, denominator 1 and the output as accumulator
+#pragma unroll
+    for (int r = 0; r < kPfRowsPerWarp; ++r) {
+      const int qr = warp * kPfRowsPerWarp + r;
+      if (qr >= nrows) continue;
+      const size_t t = (size_t)(row0 + q0 + qr);
+      m[r] = init_lse[t * H + h];
+      l[r] = m[r] > -CUDART_INF_F ? 1.f : 0.f;
+#pragma unroll
+      for (int c = 0; c < kMaxDvPerLane; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) acc[r][c] = as_f32(out[t * ldo + h * dv + d]);
+      }
+    }
+  }
   const int kv_end = ctx + q0 + nrows;                // keys this tile can see: [kv_begin, kv_end)
   // a sliding window: position i sees j with 0 <= i - j < window, so nothing before the first row's window is read
   const int kv_begin = window > 0 ? max(0, ctx + q0 - window + 1) : 0;
@@ -233,7 +251,8 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
   const int n_pool = (pool_k != nullptr && window > 0) ? max(0, (kv_end - 1 - window + 1) / pool) : 0;
   const int pool_span = (n_pool + kPfKeys - 1) & ~(kPfKeys - 1);
   const int tok_begin = kv_begin & ~(kPfKeys - 1);
-  for (int it = -pool_span; it < kv_end - tok_begin; it += kPfKeys) {
+  const int it_end = init_lse != nullptr ? 0 : kv_end - tok_begin;      // a continued softmax reads the pooled blocks only
+  for (int it = -pool_span; it < it_end; it += kPfKeys) {
     const bool pooled = it < 0;
     const int k0 = pooled ? it + pool_span : tok_begin + it;
     __syncthreads();                                  // previous block's K / V fully consumed (and Qs written)
@@ -517,13 +536,13 @@ extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias,
 
 extern "C" int b200_attn_sink_prefill_tile(void) { return kPfRows; }
 
-extern "C" int b200_attn_sink_prefill_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                           const void* v_cache, const int32_t* block_table, int max_blocks,
-                                           const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
-                                           const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
-                                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
-                                           int window, int gate_per_head, const float* head_scale, const float* pool_k,
-                                           const float* pool_v, int pool, int per_page, void* stream) {
+static int attn_sink_prefill_launch(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                    const void* v_cache, const int32_t* block_table, int max_blocks,
+                                    const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                    const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                    int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                    int window, int gate_per_head, const float* head_scale, const float* pool_k,
+                                    const float* pool_v, int pool, int per_page, const float* init_lse, void* stream) {
   if (v_ld <= 0) v_ld = dv;
   B200_REQUIRE(pool_k == nullptr || (pool_v != nullptr && window > 0 && pool > 0 && per_page == (page + pool - 1) / pool),
                "attn_sink_prefill: pooled blocks need a window, both caches and ceil(page / pool) entries per page");
@@ -545,13 +564,37 @@ extern "C" int b200_attn_sink_prefill_pool(const void* proj, int f32, int64_t ld
     attn_sink_prefill_kernel<TA, L><<<grid, kPfWarps * 32, smem, s>>>(                                             \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, cu_q,       \
         ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head,   \
-        head_scale, pool_k, pool_v, pool, per_page);                                                               \
+        head_scale, pool_k, pool_v, pool, per_page, init_lse);                                                     \
   } while (0)
   const bool wide = dv > 256;
   if (f32) { if (wide) B200_PF(float, 16); else B200_PF(float, 8); }
   else { if (wide) B200_PF(bf16, 16); else B200_PF(bf16, 8); }
 #undef B200_PF
   return b200_check_launch("b200_attn_sink_prefill");
+}
+
+extern "C" int b200_attn_sink_prefill_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                           const void* v_cache, const int32_t* block_table, int max_blocks,
+                                           const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                           const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                           int window, int gate_per_head, const float* head_scale, const float* pool_k,
+                                           const float* pool_v, int pool, int per_page, void* stream) {
+  return attn_sink_prefill_launch(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, cu_q, ctx_lens, tile_seq,
+                                  tile_q0, n_tiles, tile_rows, sink, out, ldo, H, G, dk, dv, page, scale, v_ld, window,
+                                  gate_per_head, head_scale, pool_k, pool_v, pool, per_page, nullptr, stream);
+}
+
+extern "C" int b200_attn_sink_prefill_more(const void* proj, int f32, int64_t ld, const void* k_cache,
+                                           const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles,
+                                           int tile_rows, void* out, int64_t ldo, int H, int G, int dk, int dv, int page,
+                                           float scale, int window, const float* head_scale, const float* pool_k,
+                                           const float* pool_v, int pool, int per_page, const float* init_lse, void* stream) {
+  B200_REQUIRE(init_lse != nullptr && pool_k != nullptr, "attn_sink_prefill_more: needs the first part's log-sum-exp and pooled blocks");
+  return attn_sink_prefill_launch(proj, f32, ld, -1, k_cache, k_cache, block_table, max_blocks, cu_q, ctx_lens, tile_seq,
+                                  tile_q0, n_tiles, tile_rows, nullptr, out, ldo, H, G, dk, dv, page, scale, 0, window, 0,
+                                  head_scale, pool_k, pool_v, pool, per_page, init_lse, stream);
 }
 
 extern "C" int b200_attn_sink_prefill_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,

@@ -6,7 +6,8 @@
 //                 pair i -- pairs (2i, 2i+1) ("interleaved") or (i, i + dims/2) ("half"); the rest pass unchanged.
 //                 The angle is formed and reduced to [-pi, pi] in fp64, cos / sin of the remainder in fp32;
 //   unit norm     the rotated head over its root mean square, x / sqrt(mean(x^2) + eps), no weight;
-//   factor        a constant on the queries and one on the keys (after rotation and norm).
+//   factor        a constant on the queries and one on the keys (after rotation and norm); optionally one more factor
+//                 per query head.
 //
 // Where the results go:
 //   queries       q_out rows (the projection itself = in place, or a separate fp32 buffer);
@@ -51,6 +52,7 @@ struct RotPrepArgs {
   const double* freq;
   int unit_norm;
   float eps, q_mul, k_mul;
+  const float* q_head_mul;          // optional [H]: one more factor per query head (a learned temperature)
 };
 
 template <typename TA, typename TD>
@@ -123,6 +125,7 @@ rot_prep_kernel(RotPrepArgs a) {
     }
   }
   float mul = is_q ? a.q_mul : a.k_mul;
+  if (is_q && a.q_head_mul != nullptr) mul *= a.q_head_mul[g];
   if (a.unit_norm) mul *= 1.0f / sqrtf(warp_sum(ss) / (float)width + a.eps);
 #pragma unroll
   for (int i = 0; i < kRpPairs; ++i) {
@@ -243,6 +246,7 @@ rot_prep_vec_kernel(RotPrepArgs a, int lph, int items_q, int items_v) {
       }
     }
     float mul = is_q ? a.q_mul : a.k_mul;
+    if (is_q && a.q_head_mul != nullptr) mul *= a.q_head_mul[g];
     if (a.unit_norm) {                                 // every lane takes part in the shuffles
       for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       mul *= 1.0f / sqrtf(ss / (float)dk + a.eps);
@@ -281,6 +285,16 @@ extern "C" int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_co
                              int64_t ldk, void* v_out, int64_t ldv, int dst_f32, int paged, int page, int T, int H, int G,
                              int dk, int dv, int feature, int dims, int half_layout, const double* freq, int unit_norm,
                              float eps, float q_mul, float k_mul, void* stream) {
+  return b200_rot_prep_hm(proj, src_f32, ld, q_col, k_col, v_col, positions, slots, q_out, ldq, k_out, ldk, v_out, ldv, dst_f32,
+                          paged, page, T, H, G, dk, dv, feature, dims, half_layout, freq, unit_norm, eps, q_mul, k_mul, nullptr,
+                          stream);
+}
+
+extern "C" int b200_rot_prep_hm(const void* proj, int src_f32, int64_t ld, int q_col, int k_col, int v_col,
+                                const int32_t* positions, const int32_t* slots, void* q_out, int64_t ldq, void* k_out,
+                                int64_t ldk, void* v_out, int64_t ldv, int dst_f32, int paged, int page, int T, int H, int G,
+                                int dk, int dv, int feature, int dims, int half_layout, const double* freq, int unit_norm,
+                                float eps, float q_mul, float k_mul, const float* q_head_mul, void* stream) {
   B200_REQUIRE(T >= 0 && H > 0 && G > 0 && dk > 0 && dv > 0, "rot_prep: bad shape");
   B200_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= dk && dims <= 64 * kRpPairs && dk - dims <= 32 * kRpTail,
                "rot_prep: %d rotated of %d entries (rotated <= %d, rest <= %d)", dims, dk, 64 * kRpPairs, 32 * kRpTail);
@@ -291,7 +305,7 @@ extern "C" int b200_rot_prep(const void* proj, int src_f32, int64_t ld, int q_co
   B200_REQUIRE(src_f32 ? dst_f32 : 1, "rot_prep: fp32 rows are not rounded to bf16 here");
   if (T == 0) return B200_OK;
   RotPrepArgs a{proj, ld, q_col, k_col, v_col, positions, slots, q_out, ldq, k_out, ldk, v_out, ldv, paged, page, H, G, dk, dv,
-                feature, dims, half_layout, freq, unit_norm, eps, q_mul, k_mul};
+                feature, dims, half_layout, freq, unit_norm, eps, q_mul, k_mul, q_head_mul};
   const int n_slots = k_out == nullptr ? H : H + G + (v_col >= 0 ? G : 0);
   dim3 grid(T, (n_slots + kRpWarps - 1) / kRpWarps);
   cudaStream_t s = (cudaStream_t)stream;

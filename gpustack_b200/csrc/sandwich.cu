@@ -53,7 +53,18 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
   return warp_sum(t);
 }
 
-template <typename TO>
+// 4-entry loads and stores (VEC: D a multiple of 4, 16-byte aligned fp32 rows, 8-byte aligned bf16 rows)
+__device__ __forceinline__ float4 sw_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 sw_ld4(const bf16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf16_lo(r.x), bf16_hi(r.x), bf16_lo(r.y), bf16_hi(r.y));
+}
+__device__ __forceinline__ void sw_st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void sw_st4(bf16* p, float4 v) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+template <typename TO, int V>
 __global__ void __launch_bounds__(256)
 sandwich_join_kernel(const float* x_in, const float* __restrict__ y, const float* __restrict__ y2, float ya, float yb,
                      const bf16* __restrict__ wb, float mult, const int32_t* __restrict__ rows,
@@ -62,30 +73,65 @@ sandwich_join_kernel(const float* x_in, const float* __restrict__ y, const float
   __shared__ float red[32];
   const int r = blockIdx.x;
   const size_t src = (size_t)(rows != nullptr ? rows[r] : r) * D;
+  const int i0 = threadIdx.x * V, step = blockDim.x * V;
   if (y != nullptr) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-      float v = ya * y[src + i];
-      if (y2 != nullptr) v = fmaf(yb, y2[src + i], v);
-      zrow[i] = v;
-      ss = fmaf(v, v, ss);
+    for (int i = i0; i < D; i += step) {
+      if (V == 4) {
+        float4 v = sw_ld4(y + src + i);
+        v.x *= ya; v.y *= ya; v.z *= ya; v.w *= ya;
+        if (y2 != nullptr) {
+          const float4 b = sw_ld4(y2 + src + i);
+          v.x = fmaf(yb, b.x, v.x); v.y = fmaf(yb, b.y, v.y); v.z = fmaf(yb, b.z, v.z); v.w = fmaf(yb, b.w, v.w);
+        }
+        sw_st4(zrow + i, v);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      } else {
+        float v = ya * y[src + i];
+        if (y2 != nullptr) v = fmaf(yb, y2[src + i], v);
+        zrow[i] = v;
+        ss = fmaf(v, v, ss);
+      }
     }
     const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + eps);
-    for (int i = threadIdx.x; i < D; i += blockDim.x)
-      zrow[i] = fmaf(mult, zrow[i] * rstd * (w_base + __bfloat162float(wb[i])), x_in[src + i]);
+    for (int i = i0; i < D; i += step) {
+      if (V == 4) {
+        const float4 v = sw_ld4(zrow + i), x = sw_ld4(x_in + src + i), w = sw_ld4(wb + i);
+        sw_st4(zrow + i, make_float4(fmaf(mult, v.x * rstd * (w_base + w.x), x.x), fmaf(mult, v.y * rstd * (w_base + w.y), x.y),
+                                     fmaf(mult, v.z * rstd * (w_base + w.z), x.z), fmaf(mult, v.w * rstd * (w_base + w.w), x.w)));
+      } else {
+        zrow[i] = fmaf(mult, zrow[i] * rstd * (w_base + __bfloat162float(wb[i])), x_in[src + i]);
+      }
+    }
   } else {
-    for (int i = threadIdx.x; i < D; i += blockDim.x) zrow[i] = x_in[src + i];
+    for (int i = i0; i < D; i += step) {
+      if (V == 4) sw_st4(zrow + i, sw_ld4(x_in + src + i));
+      else zrow[i] = x_in[src + i];
+    }
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {    // every thread reads back what it staged itself
-    const float z = zrow[i];
-    if (x_out != nullptr) x_out[(size_t)r * D + i] = z;
-    ss = fmaf(z, z, ss);
+  for (int i = i0; i < D; i += step) {                 // every thread reads back what it staged itself
+    if (V == 4) {
+      const float4 z = sw_ld4(zrow + i);
+      if (x_out != nullptr) sw_st4(x_out + (size_t)r * D + i, z);
+      ss = fmaf(z.x, z.x, fmaf(z.y, z.y, fmaf(z.z, z.z, fmaf(z.w, z.w, ss))));
+    } else {
+      const float z = zrow[i];
+      if (x_out != nullptr) x_out[(size_t)r * D + i] = z;
+      ss = fmaf(z, z, ss);
+    }
   }
   if (wa == nullptr || h_out == nullptr) return;
   const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + eps);
-  for (int i = threadIdx.x; i < D; i += blockDim.x)
-    sw_store(h_out + (size_t)r * D + i, zrow[i] * rstd * (w_base + __bfloat162float(wa[i])));
+  for (int i = i0; i < D; i += step) {
+    if (V == 4) {
+      const float4 z = sw_ld4(zrow + i), w = sw_ld4(wa + i);
+      sw_st4(h_out + (size_t)r * D + i, make_float4(z.x * rstd * (w_base + w.x), z.y * rstd * (w_base + w.y),
+                                                    z.z * rstd * (w_base + w.z), z.w * rstd * (w_base + w.w)));
+    } else {
+      sw_store(h_out + (size_t)r * D + i, zrow[i] * rstd * (w_base + __bfloat162float(wa[i])));
+    }
+  }
 }
 
 // Row t belongs to the sequence s with cu_seq[s] <= t < cu_seq[s + 1]
@@ -100,34 +146,63 @@ __device__ __forceinline__ int seq_of_row(const int32_t* __restrict__ cu_seq, in
 
 constexpr int kConvMaxTaps = 8;
 
-// grid (T, ceil(C / 256)); TI input element, TO output element
-template <typename TI, typename TO>
+// grid (T, ceil(C / (256 V))); TI input element, TO output element; a thread takes V neighbouring channels
+template <typename TI, typename TO, int V>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __restrict__ in_bias,
                    const float* __restrict__ w, const float* __restrict__ bias, int add_input,
                    const float* __restrict__ ring, const int32_t* __restrict__ cu_seq,
                    const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, int n_seqs, TO* out,
                    int64_t ld_out, int C, int taps) {
-  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
   const int s = seq_of_row(cu_seq, n_seqs, t);
   if (c >= C) return;
   const int ctx = ctx_lens[s], p = ctx + (t - cu_seq[s]);
   const int R = taps - 1;
-  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
-  const float cur = sw_f32(in[(size_t)t * ld_in + c]) + ib;
-  float acc = bias != nullptr ? bias[c] : 0.f;
-  if (add_input) acc += cur;
-  const float* wc = w + (size_t)c * taps;
+  float ib[V], cur[V], acc[V];
+  if (V == 4) {
+    const float4 b = in_bias != nullptr ? sw_ld4(in_bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 x = sw_ld4(in + (size_t)t * ld_in + c);
+    const float4 o = bias != nullptr ? sw_ld4(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ib[0] = b.x; ib[V > 1 ? 1 : 0] = b.y; ib[V > 2 ? 2 : 0] = b.z; ib[V > 3 ? 3 : 0] = b.w;
+    cur[0] = x.x + b.x; cur[V > 1 ? 1 : 0] = x.y + b.y; cur[V > 2 ? 2 : 0] = x.z + b.z; cur[V > 3 ? 3 : 0] = x.w + b.w;
+    acc[0] = o.x; acc[V > 1 ? 1 : 0] = o.y; acc[V > 2 ? 2 : 0] = o.z; acc[V > 3 ? 3 : 0] = o.w;
+  } else {
+    ib[0] = in_bias != nullptr ? in_bias[c] : 0.f;
+    cur[0] = sw_f32(in[(size_t)t * ld_in + c]) + ib[0];
+    acc[0] = bias != nullptr ? bias[c] : 0.f;
+  }
+#pragma unroll
+  for (int v = 0; v < V; ++v)
+    if (add_input) acc[v] += cur[v];
   for (int j = 0; j < R; ++j) {
     const int sp = p - R + j;                          // the position tap j multiplies
     if (sp < 0) continue;
-    float v;
-    if (sp >= ctx) v = sw_f32(in[(size_t)(t - (p - sp)) * ld_in + c]) + ib;
-    else v = ring[((size_t)state_slots[s] * R + (sp % R)) * C + c];
-    acc = fmaf(wc[j], v, acc);
+    float val[V];
+    if (sp >= ctx) {
+      if (V == 4) {
+        const float4 x = sw_ld4(in + (size_t)(t - (p - sp)) * ld_in + c);
+        val[0] = x.x + ib[0]; val[V > 1 ? 1 : 0] = x.y + ib[V > 1 ? 1 : 0]; val[V > 2 ? 2 : 0] = x.z + ib[V > 2 ? 2 : 0];
+        val[V > 3 ? 3 : 0] = x.w + ib[V > 3 ? 3 : 0];
+      } else {
+        val[0] = sw_f32(in[(size_t)(t - (p - sp)) * ld_in + c]) + ib[0];
+      }
+    } else {
+      const float* rp = ring + ((size_t)state_slots[s] * R + (sp % R)) * C + c;
+      if (V == 4) {
+        const float4 x = sw_ld4(rp);
+        val[0] = x.x; val[V > 1 ? 1 : 0] = x.y; val[V > 2 ? 2 : 0] = x.z; val[V > 3 ? 3 : 0] = x.w;
+      } else {
+        val[0] = rp[0];
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[(size_t)(c + v) * taps + j], val[v], acc[v]);
   }
-  acc = fmaf(wc[R], cur, acc);
-  sw_store(out + (size_t)t * ld_out + c, acc);
+#pragma unroll
+  for (int v = 0; v < V; ++v) acc[v] = fmaf(w[(size_t)(c + v) * taps + R], cur[v], acc[v]);
+  if (V == 4) sw_st4(out + (size_t)t * ld_out + c, make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]));
+  else sw_store(out + (size_t)t * ld_out + c, acc[0]);
 }
 
 // grid (n_seqs, taps - 1, ceil(C / 256))
@@ -201,12 +276,15 @@ extern "C" int b200_sandwich_join(const float* x_in, const float* y, const float
   B200_REQUIRE(smem <= 48 * 1024, "sandwich_join: D=%d exceeds the staged row (12288)", D);
   cudaStream_t s = (cudaStream_t)stream;
   const float base = zero_centred ? 1.0f : 0.0f;
-  if (h_f32)
-    sandwich_join_kernel<float><<<T, 256, smem, s>>>(x_in, y, y2, ya, yb, (const bf16*)wb, mult, rows, (const bf16*)wa, x_out,
-                                                     (float*)h_out, D, eps, base);
-  else
-    sandwich_join_kernel<bf16><<<T, 256, smem, s>>>(x_in, y, y2, ya, yb, (const bf16*)wb, mult, rows, (const bf16*)wa, x_out,
-                                                    (bf16*)h_out, D, eps, base);
+  auto al = [](const void* p, int n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+  const bool vec = D % 4 == 0 && al(x_in, 16) && al(y, 16) && al(y2, 16) && al(x_out, 16) && al(wb, 8) && al(wa, 8) &&
+                   al(h_out, h_f32 ? 16 : 8);
+#define B200_SJ(TO, V)                                                                                                  \
+  sandwich_join_kernel<TO, V><<<T, 256, smem, s>>>(x_in, y, y2, ya, yb, (const bf16*)wb, mult, rows, (const bf16*)wa, x_out, \
+                                                   (TO*)h_out, D, eps, base)
+  if (h_f32) { if (vec) B200_SJ(float, 4); else B200_SJ(float, 1); }
+  else { if (vec) B200_SJ(bf16, 4); else B200_SJ(bf16, 1); }
+#undef B200_SJ
   return b200_check_launch("b200_sandwich_join");
 }
 
@@ -219,10 +297,20 @@ extern "C" int b200_causal_conv(const void* in, int in_f32, int64_t ld_in, const
   B200_REQUIRE(taps == 1 || ring != nullptr, "causal_conv: more than one tap needs the sequences' rings");
   if (T == 0 || n_seqs == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(T, (C + 255) / 256);
+  auto al = [](const void* p, int n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+  const bool vec = C % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && al(in, in_f32 ? 16 : 8) && al(out, out_f32 ? 16 : 8) &&
+                   al(in_bias, 16) && al(bias, 16) && al(ring, 16);
+  const int V = vec ? 4 : 1;
+  dim3 grid(T, (C + 256 * V - 1) / (256 * V));
 #define B200_CC(TI, TO)                                                                                               \
-  causal_conv_kernel<TI, TO><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, ctx_lens, \
-                                                  state_slots, n_seqs, (TO*)out, ld_out, C, taps)
+  do {                                                                                                                \
+    if (vec)                                                                                                          \
+      causal_conv_kernel<TI, TO, 4><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, \
+                                                         ctx_lens, state_slots, n_seqs, (TO*)out, ld_out, C, taps);   \
+    else                                                                                                              \
+      causal_conv_kernel<TI, TO, 1><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, \
+                                                         ctx_lens, state_slots, n_seqs, (TO*)out, ld_out, C, taps);   \
+  } while (0)
   if (in_f32) { if (out_f32) B200_CC(float, float); else B200_CC(float, bf16); }
   else { if (out_f32) B200_CC(bf16, float); else B200_CC(bf16, bf16); }
 #undef B200_CC

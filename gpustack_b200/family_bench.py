@@ -1,7 +1,7 @@
-"""Side benchmark of the layer-list family (Vodavik, Danipel, Resevik) beside the closest existing model of equal layer
+"""Side benchmark of the layer-list family (Vodavik, Danipel, Resevik, Dotorax) beside the closest existing model of equal layer
 sizes (a Llama-class decoder; for Resevik also Vodavik, the other design with attention and recurrent-state layers).
 
-`python bench.py --family vodavik|danipel|resevik` prints ONE JSON line (not the serving benchmark's line; that workload and its
+`python bench.py --family vodavik|danipel|resevik|dotorax` prints ONE JSON line (not the serving benchmark's line; that workload and its
 contract are untouched).  Random weights, synthetic tokens.  Two kinds of numbers:
 
   model:   prefill tokens/s (prompts of `prompt` tokens, `seqs` at a time through runner.prefill) and decode tokens/s
@@ -22,8 +22,9 @@ import numpy as np
 import torch
 
 from . import ops
-from .config import (AttentionSpec, EngineConfig, LatentAttentionSpec, LayerListConfig, LayerSpec, LinearAttentionSpec, MLPSpec,
-                     MLSTMSpec, ModelConfig, MoESpec, RotarySpec)
+from .config import (AttentionSpec, EngineConfig, GatedLinearAttentionSpec, GatedRecurrenceSpec, LatentAttentionSpec,
+                     LayerListConfig, LayerSpec, LinearAttentionSpec, MLPSpec, MLSTMSpec, ModelConfig, MoESpec, RotarySpec,
+                     SideBySideSpec)
 
 ROOT = Path(__file__).resolve().parent.parent
 SIZES = {
@@ -95,6 +96,33 @@ def resevik_config(size: str, layers: int = 4) -> LayerListConfig:
                                                           renormalize=False, weight_on="input", act="silu"))
         specs.append(LayerSpec(mix, mlp))
     return LayerListConfig("Resevik", V, D, specs, norm_eps=1e-5, residual="parallel", norm="rms", embed_scale=D ** 0.5)
+
+
+# Dotorax at the same widths: window, pooled block, taps of the input convolution, taps of the recurrent branch
+DOTORAX = {"2k": (512, 16, 3, 4), "4k": (1024, 16, 3, 4)}
+
+
+def dotorax_config(size: str, layers: int = 4) -> LayerListConfig:
+    """attention | side by side (window + pooled blocks, recurrence of the model's width) | attention on layer 0's
+    keys and values | gated linear attention (half the heads, 64-wide keys, 128-wide values); clamped gated
+    feed-forwards of the Llama model's width."""
+    D, H, G, hd, ff, V = SIZES[size]
+    win, pool, taps, conv = DOTORAX[size]
+    specs = []
+    for i in range(layers):
+        if i % 4 in (0, 2):
+            mix = AttentionSpec(H, G, hd, hd, hd ** -0.5, qk_norm=False, qkv_bias=False, sink=False, gate=True, gate_per_head=True,
+                                rot=RotarySpec(dims=hd // 2, base=5e5, layout="half"), kv_from=0 if i % 4 == 2 else None)
+        elif i % 4 == 1:
+            left = AttentionSpec(H, G, hd, hd, hd ** -0.5, qk_norm=False, qkv_bias=False, sink=False, gate=False,
+                                 rot=RotarySpec(dims=hd // 2, base=1e4, layout="interleaved"), qk_unit_norm=True, head_temp=True,
+                                 window=win, pool=pool)
+            mix = SideBySideSpec(left, GatedRecurrenceSpec(D, H, conv), 0.6, 0.9)
+        else:
+            mix = GatedLinearAttentionSpec(H // 2, hd // 2, hd, 16.0, decay_rank=16)
+        specs.append(LayerSpec(mix, MLPSpec("dense", ff, act="clamped_swish", limit=7.0)))
+    return LayerListConfig("Dotorax", V, D, specs, norm_eps=1e-5, residual="sandwich", norm="rms_zero_centred",
+                           residual_mult=0.3, canon_taps=taps, learned_positions=True, max_position_embeddings=8192)
 
 
 def _peaks():
@@ -627,10 +655,196 @@ def _kernel_numbers_resevik(size, T, B, ctx, log):
     return res
 
 
+def _kernel_numbers_dotorax(size, T, B, ctx, log):
+    """Dotorax's kernels beside the like kernels of the closest model (Resevik: fp32 residual with a norm per layer,
+    rotary window attention, decayed linear attention) at equal sizes."""
+    D, H, G, hd, ff, V = SIZES[size]
+    win, pool, taps, conv = DOTORAX[size]
+    Hm, dkg = H // 2, hd // 2
+    hbm, flops_peak, how = _peaks()
+    flush = _Flush()
+    dev = "cuda"
+    bf, f32 = torch.bfloat16, torch.float32
+    rnd = lambda *s, dt=bf, sc=1.0: (torch.randn(*s, device=dev, dtype=f32) * sc).to(dt)   # noqa: E731
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)   # noqa: E731
+    res = {}
+
+    def put(name, new_s, new_work, like_name, like_s, like_work, kind):
+        peak = hbm if kind == "bytes" else flops_peak
+        fn, fl = new_work / new_s / peak, like_work / like_s / peak
+        res[name] = {"us": round(new_s * 1e6, 1), "frac_of_" + how + "_" + kind: round(fn, 4), "like": like_name,
+                     "like_us": round(like_s * 1e6, 1), "like_frac": round(fl, 4), "distance_ratio": round(fl / fn, 2)}
+        log(f"  {name:36s} {new_s * 1e6:9.1f} us  {fn:7.4f} of roofline | {like_name}: {like_s * 1e6:9.1f} us {fl:7.4f}"
+            f"  -> {fl / fn:5.2f}x as far")
+
+    S = max(1, T // 2048)
+    L = T // S
+    cu, ctx0, slot_s = i32(np.arange(S + 1) * L), i32(np.zeros(S)), i32(np.arange(S))
+    cud, ctxd, slot_b = i32(np.arange(B + 1)), i32(np.full(B, ctx)), i32(np.arange(B))
+    # ---- join (norm of the output, sum, norm of the sum) vs sum + norm of the one-norm-per-layer design
+    x32, ya, yb, w, w2 = rnd(T, D, dt=f32), rnd(T, D, dt=f32), rnd(T, D, dt=f32), rnd(D, sc=0.2), rnd(D, sc=0.2)
+    xb, h32 = torch.empty(T, D, device=dev, dtype=bf), torch.empty(T, D, device=dev)
+    t_new = _time(lambda: ops.sandwich_join(x32, 1e-5, y=ya, post_w=w, mult=0.3, pre_w=w2, x_out=x32, h_out=h32), flush)
+    t_like = _time(lambda: ops.add_rms_norm(x32, w, 1e-5, a=ya, x_out=x32, xb_out=xb), flush)
+    put("sandwich_join", t_new, T * D * 16.0, "add_rms_norm (1 branch)", t_like, T * D * 14.0, "bytes")
+    t_new = _time(lambda: ops.sandwich_join(x32, 1e-5, y=ya, y2=yb, ya=0.6, yb=0.9, post_w=w, mult=0.3, pre_w=w2, x_out=x32,
+                                            h_out=h32), flush)
+    t_like2 = _time(lambda: ops.add_rms_norm(x32, w, 1e-5, a=ya, b=yb, x_out=x32, xb_out=xb), flush)
+    put("sandwich_join (2 outputs)", t_new, T * D * 20.0, "add_rms_norm (2 branches)", t_like2, T * D * 18.0, "bytes")
+    # ---- input convolution with rings (+ commit) vs the same streaming norm kernel
+    cw = rnd(D, taps, dt=f32, sc=0.4)
+    ring = torch.zeros(max(S, B), taps - 1, D, device=dev)
+
+    def conv_():
+        ops.causal_conv(h32, cw, ring, cu, ctx0, slot_s, xb, add_input=True)
+        ops.conv_commit(h32, ring, cu, ctx0, slot_s, taps)
+
+    t_new = _time(conv_, flush)
+    put("causal_conv + commit (prefill)", t_new, T * D * 6.0, "add_rms_norm (1 branch)", t_like, T * D * 14.0, "bytes")
+
+    # ---- attention with one gate per head (half rotation): generic kernel vs the tcgen05 kernel with sink + element gate
+    nblk = (B * ctx + T) // 16 + 8
+    Wp = (H + 2 * G) * hd + 8
+    proj = rnd(T, Wp)
+    kc, vc = rnd(nblk, G, 16, hd), rnd(nblk, G, 16, hd)
+    pos, slots = i32(np.arange(T) % L), i32(np.arange(T) + 16)
+    freq = torch.tensor(RotarySpec(dims=hd // 2, base=5e5).frequencies()[0], dtype=torch.float64, device=dev)
+    t_new = _time(lambda: ops.rot_prep(proj, 0, H * hd, (H + G) * hd, pos, slots, proj, kc, vc, H, G, hd, hd, paged=True,
+                                       rot_dims=hd // 2, half_layout=True, freq=freq), flush)
+    projr = rnd(T, (H + G) * hd)
+    t_like = _time(lambda: ops.rot_prep(projr, 0, H * hd, -1, pos, slots, projr, kc, vc, H, G, hd, hd, paged=True,
+                                        rot_dims=hd // 2, half_layout=False, freq=freq, unit_norm=True, eps=1e-5), flush)
+    put("rot_prep (half, own values)", t_new, T * (2 * H + 4 * G) * hd * 2.0, "rot_prep (Resevik attention)", t_like,
+        T * (2 * H + 3 * G) * hd * 2.0, "bytes")
+    tile = ops.attn_sink_prefill_tile()
+    ts_, tq_ = ops.build_prefill_tiles([L] * S, tile, [0] * S)
+    nb = (L + 15) // 16
+    bt = i32(np.arange(S * nb).reshape(S, nb) + 1)
+    out = torch.empty(T, H * hd, device=dev, dtype=bf)
+    ts_d, tq_d = i32(ts_), i32(tq_)
+    gate_col = (H + 2 * G) * hd
+    tile_tc = ops.attn_prefill_tile(H, G)
+    tt_, tqq_ = ops.build_prefill_tiles([L] * S, tile_tc, [0] * S)
+    tt_d, tqq_d = i32(tt_), i32(tqq_)
+    t_new = _time(lambda: ops.paged_attn_prefill_ex(proj, Wp, kc, vc, bt, cu, ctx0, tt_d, tqq_d, out, H, G, hd, hd ** -0.5,
+                                                    gate=proj[:, gate_col:], gate_per_head=True), flush)
+    Wv = (H + 2 * G) * hd + H * hd
+    projv = rnd(T, Wv)
+    sink = rnd(H, dt=f32)
+    t_tc = _time(lambda: ops.paged_attn_prefill_ex(projv, Wv, kc, vc, bt, cu, ctx0, tt_d, tqq_d, out, H, G, hd, hd ** -0.5,
+                                                   sink=sink, gate=projv[:, gate_col:]), flush)
+    full = 4.0 * S * (L * L / 2) * H * hd
+    put("attention prefill, head gate", t_new, full, "attention prefill, sink + gate tc", t_tc, full, "flops")
+    # ---- window + pooled blocks vs the tcgen05 kernel with a window
+    per_page = -(-16 // pool)
+    pk, pv = torch.zeros(nblk, G, per_page, hd, device=dev), torch.zeros(nblk, G, per_page, hd, device=dev)
+    temp = rnd(H, dt=f32, sc=0.1) + 1.0
+    t_pool = _time(lambda: ops.kv_pool_update(kc, vc, pk, pv, bt, cu, ctx0, S, L, pool), flush)
+    lse = torch.empty(T, H, device=dev)
+
+    def window_then_pooled():
+        ops.paged_attn_prefill_ex(proj, Wp, kc, vc, bt, cu, ctx0, tt_d, tqq_d, out, H, G, hd, hd ** -0.5, window=win, lse_out=lse)
+        ops.attn_sink_prefill_more(proj, kc, bt, cu, ctx0, tt_d, tqq_d, out, lse, H, G, hd, hd, hd ** -0.5, tile_tc, win, None,
+                                   (pk, pv, pool))
+
+    t_new = _time(window_then_pooled, flush)
+    t_gen = _time(lambda: ops.attn_sink_prefill(proj, -1, kc, vc, bt, cu, ctx0, ts_d, tq_d, None, out, H, G, hd, hd, hd ** -0.5,
+                                                window=win, head_scale=temp, pool=(pk, pv, pool)), flush, iters=3, warm=1)
+    t_win = _time(lambda: ops.paged_attn_prefill_ex(projr, projr.shape[1], kc, kc, bt, cu, ctx0, tt_d, tqq_d, out, H, G, hd,
+                                                    hd ** -0.5, window=win), flush)
+    pairs_w = S * sum(min(i + 1, win) for i in range(L))
+    pairs_p = pairs_w + S * sum(max(0, (i - win + 1) // pool) for i in range(L))
+    put("attention prefill, window + pooled", t_new, 4.0 * pairs_p * H * hd, "attention prefill, window tc", t_win,
+        4.0 * pairs_w * H * hd, "flops")
+    put("attention prefill, window + pooled (generic kernel alone)", t_gen, 4.0 * pairs_p * H * hd, "attention prefill, window tc",
+        t_win, 4.0 * pairs_w * H * hd, "flops")
+    put("kv_pool_update (prefill)", t_pool, T * G * hd * 2 * 2.0 * (1 + 2.0 / pool), "rot_prep (Resevik attention)", t_like,
+        T * (2 * H + 3 * G) * hd * 2.0, "bytes")
+    # ---- decode attention
+    nbd = (ctx + 16) // 16
+    btd = i32(np.arange(B * nbd).reshape(B, nbd) % (nblk - 1) + 1)
+    lens = i32(np.full(B, ctx))
+    outd = torch.empty(B, H * hd, device=dev, dtype=bf)
+    pB = proj[:B]
+    splits = ops.attn_decode_splits(B, G, ctx + 16)
+    ws = ops.attn_decode_workspace(B, H, hd, splits, dev)
+    t_new = _time(lambda: ops.paged_attn_decode(pB, Wp, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=splits,
+                                                workspace=ws, gate=pB[:, gate_col:], gate_per_head=True), flush)
+    pvB, gB = projv[:B], projv[:B, gate_col:]
+    t_like_d = _time(lambda: ops.paged_attn_decode(pvB, Wv, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=splits,
+                                                   workspace=ws, sink=sink, gate=gB), flush)
+    kvb = B * ctx * G * hd * 2 * 2.0
+    put("attention decode, head gate", t_new, kvb, "attention decode, sink + gate tc", t_like_d, kvb, "bytes")
+    t_new = _time(lambda: ops.attn_sink_decode(pB, -1, kc, vc, btd, lens, None, outd, H, G, hd, hd, hd ** -0.5, window=win,
+                                               head_scale=temp, pool=(pk, pv, pool)), flush)
+    sp_w = ops.attn_decode_splits(B, G, min(ctx + 16, win))
+    ws_w = ops.attn_decode_workspace(B, H, hd, sp_w, dev)
+    prB = projr[:B]
+    t_like_w = _time(lambda: ops.paged_attn_decode(prB, projr.shape[1], kc, kc, btd, lens, outd, H, G, hd, hd ** -0.5,
+                                                   num_splits=sp_w, workspace=ws_w, window=win), flush)
+    kvw = B * min(ctx, win) * G * hd * 2 * 2.0
+    kvp = kvw + B * max(0, (ctx - win) // pool) * G * hd * 2 * 4.0
+    put("attention decode, window + pooled", t_new, kvp, "attention decode, window tc", t_like_w, kvw, "bytes")
+
+    # ---- gated diagonal recurrence (conv + gate projections + scan) vs the decayed linear attention's closing kernel
+    Wd = D
+    pr = rnd(T, 2 * Wd, sc=0.5)
+    rb = rnd(2 * Wd, dt=f32, sc=0.1)
+    cwr, cbr = rnd(Wd, conv, dt=f32, sc=0.4), rnd(Wd, dt=f32, sc=0.1)
+    ringr = torch.zeros(max(S, B), conv - 1, Wd, device=dev)
+    u = torch.empty(T, Wd, device=dev)
+    gw = rnd(2 * H, Wd // H, Wd // H, sc=(Wd // H) ** -0.5)
+    gates = torch.empty(T, 2 * Wd, device=dev)
+    gb, lam = rnd(2 * Wd, dt=f32, sc=0.3), rnd(Wd, dt=f32)
+    Sr = torch.zeros(max(S, B), Wd, device=dev)
+    outr = torch.empty(T, Wd, device=dev, dtype=bf)
+    n = Wd // H
+    t_conv = _time(lambda: ops.causal_conv(pr[:, Wd:], cwr, ringr, cu, ctx0, slot_s, u, add_input=False, in_bias=rb[Wd:], bias=cbr),
+                   flush)
+
+    def gates_():
+        ops.head_linear(u, gw[:H], gates[:, :Wd], H, n=n, k=n, x_head=n, out_head=n)
+        ops.head_linear(u, gw[H:], gates[:, Wd:], H, n=n, k=n, x_head=n, out_head=n)
+
+    t_gates = _time(gates_, flush)
+    rws = ops.gated_recurrence_workspace(T, max(S, B), Wd, dev)
+    t_scan = _time(lambda: ops.gated_recurrence_scan(u, gates, gb, lam, pr, 0, rb[:Wd], cu, ctx0, slot_s, Sr, outr, 8.0, max_len=L,
+                                                     workspace=rws), flush)
+    o_raw = rnd(T, Hm * hd, dt=f32)
+    pl = rnd(T, 4 * Hm * hd, sc=0.5)
+    mo = torch.empty(T, Hm * hd, device=dev, dtype=bf)
+    t_out = _time(lambda: ops.linattn_out(o_raw, pl, 3 * Hm * hd, None, mo, Hm, hd, 1e-5, False, "silu"), flush)
+    put("recurrence: causal_conv", t_conv, T * Wd * 6.0, "linattn_out (per head)", t_out, T * Hm * hd * 8.0, "bytes")
+    put("recurrence: gate projections (fp32)", t_gates, T * Wd * 12.0, "linattn_out (per head)", t_out, T * Hm * hd * 8.0, "bytes")
+    put("recurrence: scan (prefill)", t_scan, T * Wd * 16.0, "linattn_out (per head)", t_out, T * Hm * hd * 8.0, "bytes")
+    uB, gB_, prB_, outB = u[:B], gates[:B], pr[:B], outr[:B]
+    t_scan_d = _time(lambda: ops.gated_recurrence_scan(uB, gB_, gb, lam, prB_, 0, rb[:Wd], cud, ctxd, slot_b, Sr, outB, 8.0), flush)
+    put("recurrence: scan (decode)", t_scan_d, B * Wd * 24.0, "linattn_out (per head)", t_out, T * Hm * hd * 8.0, "bytes")
+
+    # ---- gated linear attention vs decayed linear attention (fixed decay per head) at equal head shapes
+    xg = rnd(T, 2 * Hm * dkg + Hm * hd, dt=f32, sc=0.5)
+    z = rnd(T, Hm * dkg, dt=f32, sc=2.0) + 2.0
+    Sg = torch.zeros(max(S, B), Hm, hd, dkg, device=dev)
+    og = torch.empty(T, Hm * hd, device=dev)
+    decay = torch.tensor([0.97] * Hm, dtype=f32, device=dev)
+    t_new = _time(lambda: ops.gla_scan(xg, 0, Hm * dkg, 2 * Hm * dkg, z, 1.0 / 16, cu, ctx0, slot_s, Sg, og, Hm, dkg, hd), flush,
+                  iters=3, warm=1)
+    t_like = _time(lambda: ops.linattn_scan(xg, 0, Hm * dkg, 2 * Hm * dkg, decay, cu, ctx0, slot_s, Sg, og, Hm, dkg, hd, max_len=L),
+                   flush)
+    wl = 4.0 * T * Hm * dkg * hd
+    put("gla_scan (prefill)", t_new, wl, "linattn_scan (prefill, chunk)", t_like, wl, "flops")
+    xB, zB, oB = xg[:B], z[:B], og[:B]
+    t_new = _time(lambda: ops.gla_scan(xB, 0, Hm * dkg, 2 * Hm * dkg, zB, 1.0 / 16, cud, ctxd, slot_b, Sg, oB, Hm, dkg, hd), flush)
+    t_like = _time(lambda: ops.linattn_scan(xB, 0, Hm * dkg, 2 * Hm * dkg, decay, cud, ctxd, slot_b, Sg, oB, Hm, dkg, hd, max_len=1),
+                   flush)
+    put("gla_scan (decode)", t_new, B * Hm * dkg * hd * 8.0, "linattn_scan (decode)", t_like, B * Hm * dkg * hd * 8.0, "bytes")
+    return res
+
+
 FAMILIES = {"vodavik": (vodavik_config, _kernel_numbers), "danipel": (danipel_config, _kernel_numbers_danipel),
-            "resevik": (resevik_config, _kernel_numbers_resevik)}
+            "resevik": (resevik_config, _kernel_numbers_resevik), "dotorax": (dotorax_config, _kernel_numbers_dotorax)}
 # a family whose closest existing model is another layer-list design is measured beside that one too
-CLOSEST = {"resevik": ("vodavik", vodavik_config)}
+CLOSEST = {"resevik": ("vodavik", vodavik_config), "dotorax": ("resevik", resevik_config)}
 
 
 def run(sizes=("2k", "4k"), seqs=4, prompt=2048, batch=64, decode_steps=32, log=None, family="vodavik"):

@@ -87,11 +87,16 @@ class LayerListRunner(ModelRunner):
         self.fast_prefill = {l: bf and m.tile_sized and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim) for l, m in attn}
         base = ops.attn_sink_prefill_tile()
         # ONE tile list serves every layer of a step: the tile size most tensor-core layers want (ties: the larger)
-        tiles = [ops.attn_prefill_tile(m.heads, m.kv_heads) for l, m in attn if self.fast_prefill[l]]
+        tiles = [ops.attn_prefill_tile(m.heads, m.kv_heads) for l, m in attn
+                 if self.fast_prefill[l] or (bf and m.pool and m.dim == m.vdim and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim))]
         self.prefill_tile = max(set(tiles), key=lambda t: (tiles.count(t), t)) if tiles else base
         for l, m in attn:
             if self.fast_prefill[l] and ops.attn_prefill_tile(m.heads, m.kv_heads) != self.prefill_tile:
                 self.fast_prefill[l] = False
+        # a window with pooled blocks: the window's tokens on the tcgen05 kernel (which hands over every row's log-sum-exp),
+        # the pooled blocks by the generic kernel that continues that softmax
+        self.pool_tc = {l: bool(bf and ops.LAYER_LIST_TC and m.pool and m.dim == m.vdim and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim)
+                                and ops.attn_prefill_tile(m.heads, m.kv_heads) == self.prefill_tile) for l, m in attn}
         if self.prefill_tile % base:
             raise B200Error("prefill tile sizes of the attention kernels do not nest")
         self._dec_ws = {}
@@ -139,6 +144,8 @@ class LayerListRunner(ModelRunner):
         self.gates = e(T * max(1, self.gate_width), dt=torch.float32)
         self.o_raw = e(T * max(1, self.rec_width), dt=torch.float32)
         self.lin32 = e(T * max(1, self.lin_width), dt=torch.float32)   # prepared q | k | v rows of a linear-attention mixer
+        gdr = [l.mixer.right.width for l in self.mcfg.layers if l.mixer.kind == "side_by_side"]
+        self.rec_ws = ops.gated_recurrence_workspace(T, self.max_seqs, max(gdr), dev) if gdr else None
         if self.sandwich:
             self.y2 = e(T, D, dt=torch.float32)           # the second output of a side-by-side mixer
             self.h32 = e(T, D, dt=torch.float32)          # a sublayer's normed input before its convolution
@@ -404,7 +411,7 @@ class LayerListRunner(ModelRunner):
                 if nt and self.fast_prefill[li]:
                     ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, out[:Tp], H, G, dk,
                                               m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None,
-                                              window=m.window)
+                                              window=m.window, gate_per_head=m.gate_per_head)
                 elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
                                           H, G, dk, dv, m.scale, tile_rows=self.prefill_tile, window=m.window,
@@ -413,7 +420,8 @@ class LayerListRunner(ModelRunner):
                     splits, ws = self._decode_plan(Bd, m)
                     ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
                                           num_splits=splits, workspace=ws, sink=lw.sink,
-                                          gate=proj[Tp:T, gate_col:] if m.gate else None, window=m.window)
+                                          gate=proj[Tp:T, gate_col:] if m.gate else None, window=m.window,
+                                          gate_per_head=m.gate_per_head)
                 elif Bd:
                     ops.attn_sink_decode(proj[Tp:T], gate_col, kc, vc, bt_d, lens_d, lw.sink, out[Tp:T], H, G, dk, dv,
                                          m.scale, window=m.window, gate_per_head=m.gate_per_head, head_scale=lw.head_scale)
@@ -471,10 +479,17 @@ class LayerListRunner(ModelRunner):
         a, r = m.left, m.right
         eps = self.mcfg.norm_eps
         H, G, dk, dv, W = a.heads, a.kv_heads, a.dim, a.vdim, r.width
-        left, right = out[:, :a.out_width], out[:, a.out_width:]
+        # the two sides' outputs, each contiguous (the tensor-core attention kernel writes whole rows of heads)
+        left = self.mix_out[:T * a.out_width].view(T, a.out_width)
+        right = self.mix_out[T * a.out_width:T * (a.out_width + W)].view(T, W)
         kc, vc = self.k_cache[l], self.v_cache[l]
+        li = self.runs[l][0]
+        tc = nt and self.pool_tc.get(li, False)
+        # the per-head temperature rides in the query (tensor-core route: its kernel has one scale) or in the kernel
         ops.rot_prep(proj, 0, H * dk, (H + G) * dk, self._pos, self._slots, proj, kc, vc, H, G, dk, dv, paged=True,
-                     rot_dims=a.rot.dims, half_layout=a.rot.layout == "half", freq=lw.rot_freq, unit_norm=a.qk_unit_norm, eps=eps)
+                     rot_dims=a.rot.dims, half_layout=a.rot.layout == "half", freq=lw.rot_freq, unit_norm=a.qk_unit_norm, eps=eps,
+                     q_head_mul=lw.head_scale if (tc and lw.head_scale is not None) else None)
+        hs = None if tc else lw.head_scale
         pool = None
         if a.pool:
             pool = (self.pool_k[l], self.pool_v[l], a.pool)
@@ -482,12 +497,19 @@ class LayerListRunner(ModelRunner):
                 ops.kv_pool_update(kc, vc, pool[0], pool[1], bt_p, cu_p, ctx_p, cu_p.shape[0] - 1, Tp, a.pool)
             if Bd:
                 ops.kv_pool_update(kc, vc, pool[0], pool[1], bt_d, None, lens_d, Bd, 1, a.pool)
-        if nt:
+        if tc:
+            lse = self._view(self.gates, Tp, H)
+            ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, left[:Tp], H, G, dk, a.scale,
+                                      window=a.window, lse_out=lse)
+            ops.attn_sink_prefill_more(proj[:Tp], kc, bt_p, cu_p, ctx_p, ts, tq, left[:Tp], lse, H, G, dk, dv, a.scale,
+                                       self.prefill_tile, a.window, None, pool)
+            self.stats["kernel_launches"] += 1
+        elif nt:
             ops.attn_sink_prefill(proj[:Tp], -1, kc, vc, bt_p, cu_p, ctx_p, ts, tq, None, left[:Tp], H, G, dk, dv, a.scale,
-                                  tile_rows=self.prefill_tile, window=a.window, head_scale=lw.head_scale, pool=pool)
+                                  tile_rows=self.prefill_tile, window=a.window, head_scale=hs, pool=pool)
         if Bd:
             ops.attn_sink_decode(proj[Tp:T], -1, kc, vc, bt_d, lens_d, None, left[Tp:T], H, G, dk, dv, a.scale,
-                                 window=a.window, head_scale=lw.head_scale, pool=pool)
+                                 window=a.window, head_scale=hs, pool=pool)
         y_col = a.q_width + G * (dk + dv)
         x_in = proj[:, y_col + W:y_col + 2 * W]
         S, ring = self.state[l]
@@ -501,7 +523,7 @@ class LayerListRunner(ModelRunner):
         ops.head_linear(u, lw.rec_gates[:r.blocks], gates[:, :W], r.blocks, n=n, k=n, x_head=n, out_head=n)
         ops.head_linear(u, lw.rec_gates[r.blocks:], gates[:, W:], r.blocks, n=n, k=n, x_head=n, out_head=n)
         ops.gated_recurrence_scan(u, gates, lw.rec_gate_bias, lw.rec_lam, proj, y_col, lw.rec_bias[:W], cu_all, ctx_all,
-                                  slots_all, S, right, r.gate_c)
+                                  slots_all, S, right, r.gate_c, max_len=Tp if Tp else 1, workspace=self.rec_ws)
         ops.linear(left, lw.o, self.y[:T])
         ops.linear(right, lw.o2, self.y2[:T])
         self._pending = (self.y[:T], self.y2[:T], m.left_scale, m.right_scale, lw.norm1b)

@@ -143,8 +143,21 @@ SIGNATURES = {
                                            _i32, _i32, _vp]),
     "b200_attn_sink_decode_pool": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
                                           _i32, _i32, _i32, _f32, _i64, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "b200_paged_attn_prefill_hg": (_i32, [_vp, _i64, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp,
+                                          _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b200_paged_attn_prefill_lse": (_i32, [_vp, _i64, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp,
+                                           _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp, _vp]),
+    "b200_attn_sink_prefill_more": (_i32, [_vp, _i32, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32,
+                                           _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "b200_rot_prep_hm": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i32, _i32, _i32,
+                                _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _f32, _vp, _vp]),
+    "b200_paged_attn_decode_hg": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
+                                         _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp]),
     "b200_gated_recurrence_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32,
                                           _i32, _f32, _vp]),
+    "b200_gated_recurrence_chunk_rows": (_i32, []),
+    "b200_gated_recurrence_scan_chunked": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                                  _i32, _i32, _f32, _i32, _i32, _vp, _i64, _vp]),
     "b200_gla_scan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
                              _vp]),
 }

@@ -367,17 +367,17 @@ def attn_decode_workspace(B, Hq, D, num_splits, device) -> torch.Tensor:
 
 
 def paged_attn_decode(q, q_stride, k_cache, v_cache, block_table, seq_lens, out, Hq, Hkv, D, scale,
-                      num_splits=1, workspace=None, sink=None, gate=None, window: int = 0):
+                      num_splits=1, workspace=None, sink=None, gate=None, window: int = 0, gate_per_head: bool = False):
     """q: [B, >=Hq*D] view into the qkv buffer (row stride q_stride elements).  sink [Hq] fp32: softmax sink;
-    gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate); window > 0: the
-    row at position n - 1 sees keys [n - window, n)."""
+    gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate) -- with gate_per_head
+    the view holds ONE number per head, [B, >=Hq]; window > 0: the row at position n - 1 sees keys [n - window, n)."""
     B = seq_lens.shape[0]
     _req(block_table, torch.int32, "block_table"); _req(seq_lens, torch.int32, "seq_lens")
-    check(load().b200_paged_attn_decode_win(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
-                                            block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
-                                            num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
-                                            0 if gate is None else gate.stride(0), int(window), _stream()),
-          "paged_attn_decode")
+    check(load().b200_paged_attn_decode_hg(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
+                                           block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
+                                           num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
+                                           0 if gate is None else gate.stride(0), int(window), 1 if gate_per_head else 0,
+                                           _stream()), "paged_attn_decode")
     return out
 
 
@@ -406,15 +406,17 @@ def attn_prefill_tc_covers(Hq, Hkv, D) -> bool:
 
 
 def paged_attn_prefill_ex(q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, out, Hq, Hkv, D,
-                          scale, sink=None, gate=None, window: int = 0):
-    """The tcgen05 prefill kernel with a softmax sink ([Hq] fp32), a sigmoid output gate (bf16 view [T, >=Hq*D])
-    and / or a sliding window (position i sees j with 0 <= i - j < window); only for shapes
-    attn_prefill_tc_covers() accepts, tiles of attn_prefill_tile(Hq, Hkv) rows."""
-    check(load().b200_paged_attn_prefill_win(_p(q), q_stride, q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0],
+                          scale, sink=None, gate=None, window: int = 0, gate_per_head: bool = False, lse_out=None):
+    """The tcgen05 prefill kernel with a softmax sink ([Hq] fp32), a sigmoid output gate (bf16 view [T, >=Hq*D], or
+    [T, >=Hq] with gate_per_head: one number per head) and / or a sliding window (position i sees j with
+    0 <= i - j < window); only for shapes attn_prefill_tc_covers() accepts, tiles of attn_prefill_tile(Hq, Hkv) rows."""
+    if lse_out is not None:       # fp32 [T, Hq]: every row's log-sum-exp, for attn_sink_prefill_more
+        _req(lse_out, torch.float32, "lse_out")
+    check(load().b200_paged_attn_prefill_lse(_p(q), q_stride, q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0],
                                              _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
                                              _p(tile_q0), tile_seq.shape[0], _p(out), Hq, Hkv, D, k_cache.shape[2], scale,
                                              _p(sink), _p(gate), 0 if gate is None else gate.stride(0), int(window),
-                                             _stream()), "paged_attn_prefill_ex")
+                                             1 if gate_per_head else 0, _p(lse_out), _stream()), "paged_attn_prefill_ex")
     return out
 
 
@@ -562,6 +564,22 @@ def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_l
     return out
 
 
+def attn_sink_prefill_more(proj, k_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, out, init_lse, H, G, dk, dv, scale,
+                           tile_rows: int, window: int, head_scale, pool):
+    """Continues a softmax over the pooled blocks: `out` holds the normalised attention over the window's tokens (another
+    kernel's), init_lse [T, H] its log-sum-exp; `out` is rewritten with the joint result.  head_scale multiplies `scale`
+    here only: the first part must have been run with the same per-head scale."""
+    _cuda(proj, k_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, out, init_lse, head_scale)
+    _req(init_lse, torch.float32, "init_lse")
+    pk, pv, pn, ppp = _pool_args(pool, k_cache, dk, dv)
+    check(load().b200_attn_sink_prefill_more(_p(proj), _is_f32(proj), proj.stride(0), _p(k_cache), _p(block_table),
+                                             block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq), _p(tile_q0),
+                                             tile_seq.shape[0], tile_rows, _p(out), out.stride(0), H, G, dk, dv,
+                                             k_cache.shape[2], scale, int(window), _p(head_scale), pk, pv, pn, ppp, _p(init_lse),
+                                             _stream()), "attn_sink_prefill_more")
+    return out
+
+
 def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale,
                      v_ld: int = 0, window: int = 0, gate_per_head: bool = False, head_scale=None, pool=None):
     _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out, head_scale)
@@ -614,10 +632,10 @@ def add_rms_norm(x_in, w, eps: float, a=None, b=None, c=None, x_out=None, xb_out
 
 def rot_prep(proj, q_col: int, k_col: int, v_col: int, positions, slots, q_out, k_out, v_out, H, G, dk, dv, *,
              paged: bool, feature: Optional[str] = None, rot_dims: int = 0, half_layout: bool = False, freq=None,
-             unit_norm: bool = False, eps: float = 0.0, q_mul: float = 1.0, k_mul: float = 1.0):
+             unit_norm: bool = False, eps: float = 0.0, q_mul: float = 1.0, k_mul: float = 1.0, q_head_mul=None):
     """Per-head feature map / rotation / unit norm / factor of a fused projection's q, k (and v) heads
     (csrc/rot_prep.cu).  paged: k_out / v_out are cache pages [blocks, G, page, width] written at slots[t]; otherwise
-    row buffers.  v_col < 0: the values are the keys as projected."""
+    row buffers.  v_col < 0: the values are the keys as projected.  q_head_mul: fp32 [H], one more factor per query head."""
     _cuda(proj, positions, slots, q_out, k_out, v_out, freq)
     if freq is not None:
         _req(freq, torch.float64, "freq")
@@ -627,11 +645,12 @@ def rot_prep(proj, q_col: int, k_col: int, v_col: int, positions, slots, q_out, 
     if k_out is None:          # a mixer that reads another layer's keys and values: queries only
         paged, v_out = False, None
     page = k_out.shape[2] if paged else 0
-    check(load().b200_rot_prep(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(positions), _p(slots),
+    _cuda(q_head_mul)
+    check(load().b200_rot_prep_hm(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(positions), _p(slots),
                                _p(q_out), q_out.stride(0), _p(k_out), 0 if (paged or k_out is None) else k_out.stride(0), _p(v_out),
                                0 if (paged or v_out is None) else v_out.stride(0), _is_f32(dst), 1 if paged else 0, page,
                                proj.shape[0], H, G, dk, dv, {None: 0, "silu": 1}[feature], rot_dims, 1 if half_layout else 0,
-                               _p(freq), 1 if unit_norm else 0, eps, q_mul, k_mul, _stream()), "rot_prep")
+                               _p(freq), 1 if unit_norm else 0, eps, q_mul, k_mul, _p(q_head_mul), _stream()), "rot_prep")
 
 
 def linattn_scan(x, q_col: int, k_col: int, v_col: int, decay, cu_seq, ctx_lens, state_slots, S, o_raw, H, dk, dv,
@@ -712,15 +731,29 @@ def kv_pool_update(k_cache, v_cache, pool_k, pool_v, block_table, cu_q, ctx_lens
                                      pool_k.shape[2], _stream()), "kv_pool_update")
 
 
+def gated_recurrence_workspace(max_tokens: int, max_seqs: int, W: int, device) -> torch.Tensor:
+    """Workspace of the chunked scan for steps of up to max_tokens rows in up to max_seqs sequences."""
+    rows = max_tokens // load().b200_gated_recurrence_chunk_rows() + max_seqs + 1
+    return torch.empty(2 * rows * W, dtype=torch.float32, device=device)
+
+
 def gated_recurrence_scan(u, gates, gate_bias, lam, proj, y_col: int, y_bias, cu_seq, ctx_lens, state_slots, S, out,
-                          gate_c: float):
-    """Gated diagonal recurrence over every sequence's new rows (csrc/gated_recurrence.cu)."""
-    _cuda(u, gates, gate_bias, lam, proj, y_bias, cu_seq, ctx_lens, state_slots, S, out)
+                          gate_c: float, max_len: int = 1, workspace=None):
+    """Gated diagonal recurrence over every sequence's new rows (csrc/gated_recurrence.cu).  max_len: an upper bound of the
+    new rows per sequence; prompt portions run in chunks side by side when a workspace is given."""
+    _cuda(u, gates, gate_bias, lam, proj, y_bias, cu_seq, ctx_lens, state_slots, S, out, workspace)
     for t_, n_ in ((u, "u"), (gates, "gates"), (gate_bias, "gate_bias"), (lam, "lam"), (y_bias, "y_bias"), (S, "S")):
         _req(t_, torch.float32, n_)
     W = u.shape[1]
     if out.dtype != proj.dtype:
         raise B200Error("gated_recurrence_scan: projection and output share one element type")
+    if workspace is not None and max_len > 8:
+        check(load().b200_gated_recurrence_scan_chunked(_p(u), _p(gates), _p(gate_bias), _p(lam), _p(proj), _is_f32(proj),
+                                                        proj.stride(0), y_col, _p(y_bias), _p(cu_seq), _p(ctx_lens),
+                                                        _p(state_slots), _p(S), _p(out), out.stride(0), state_slots.shape[0], W,
+                                                        gate_c, u.shape[0], int(max_len), _p(workspace), workspace.numel(),
+                                                        _stream()), "gated_recurrence_scan_chunked")
+        return out
     check(load().b200_gated_recurrence_scan(_p(u), _p(gates), _p(gate_bias), _p(lam), _p(proj), _is_f32(proj), proj.stride(0),
                                             y_col, _p(y_bias), _p(cu_seq), _p(ctx_lens), _p(state_slots), _p(S), _p(out),
                                             out.stride(0), state_slots.shape[0], W, gate_c, _stream()), "gated_recurrence_scan")

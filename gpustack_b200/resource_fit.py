@@ -85,6 +85,7 @@ def _layer_list_workspace(m, e: EngineConfig) -> int:
     par = 4 * (1 + (1 if m.loop_times > 1 else 0)) if m.residual == "parallel" else 0    # second branch output, embedding copy
     if m.residual == "sandwich":
         par = 8                                                                          # second output, normed input (fp32)
+        routed += 8 * (T // 64 + S + 1) * max([x.mixer.right.width for x in m.layers if x.mixer.kind == "side_by_side"] or [0])
     act = T * (D * (4 * getattr(m, "n_streams", 1) + a + 4 + par) + (proj + mix + ff + lat) * a + (gates + rec + lin) * 4) + routed
     max_len = e.max_model_len or m.max_position_embeddings
     staging = (3 * T + 10 * S + 3 * S_smp + S * math.ceil(max_len / e.block_size) + 2 * T) * 4

@@ -467,12 +467,54 @@ int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld, int gate_c
                                void* out, int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
                                int window, int gate_per_head, const float* head_scale, const float* pool_k,
                                const float* pool_v, int pool, int per_page, void* stream);
+/* The tensor-core attention kernels with an output gate of ONE number per head (gate[token][head]) when
+ * gate_per_head != 0; otherwise as b200_paged_attn_prefill_win / _decode_win. */
+int b200_paged_attn_prefill_hg(const void* q, int64_t q_stride, int num_tokens, const void* k_cache, const void* v_cache,
+                               int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                               const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
+                               void* out, int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                               const void* gate, int64_t gate_stride, int window, int gate_per_head, void* stream);
+/* ... and lse_out [T][Hq] (fp32, may be NULL): every row's log-sum-exp, for a caller that continues the softmax over
+ * more keys (b200_attn_sink_prefill_more). */
+int b200_paged_attn_prefill_lse(const void* q, int64_t q_stride, int num_tokens, const void* k_cache, const void* v_cache,
+                                int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                                const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
+                                void* out, int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                const void* gate, int64_t gate_stride, int window, int gate_per_head, float* lse_out,
+                                void* stream);
+int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                              const int32_t* block_table, int max_blocks, const int32_t* seq_lens, void* out,
+                              void* workspace, int num_splits, int B, int Hq, int Hkv, int D, int block_size, float scale,
+                              const float* sink, const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                              void* stream);
+/* b200_attn_sink_prefill_pool that CONTINUES a softmax: the window's tokens have been attended by another kernel, which
+ * left its normalised output in `out` and every row's log-sum-exp in init_lse [T][H]; only the pooled blocks are read
+ * here and `out` is rewritten with the joint result. */
+int b200_attn_sink_prefill_more(const void* proj, int f32, int64_t ld, const void* k_cache, const int32_t* block_table,
+                                int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                const int32_t* tile_q0, int n_tiles, int tile_rows, void* out, int64_t ldo, int H, int G, int dk,
+                                int dv, int page, float scale, int window, const float* head_scale, const float* pool_k,
+                                const float* pool_v, int pool, int per_page, const float* init_lse, void* stream);
+/* b200_rot_prep with one more factor per query head (q_head_mul [H] fp32, may be NULL). */
+int b200_rot_prep_hm(const void* proj, int src_f32, int64_t ld, int q_col, int k_col, int v_col, const int32_t* positions,
+                     const int32_t* slots, void* q_out, int64_t ldq, void* k_out, int64_t ldk, void* v_out, int64_t ldv,
+                     int dst_f32, int paged, int page, int T, int H, int G, int dk, int dv, int feature, int dims,
+                     int half_layout, const double* freq, int unit_norm, float eps, float q_mul, float k_mul,
+                     const float* q_head_mul, void* stream);
 /* Gated diagonal recurrence over every sequence's new rows: u [T][W], gates [T][2W] (recurrence | input gate
  * pre-activations), S [slots][W]; out = S_t * gelu_tanh(proj[t][y_col + c] + y_bias[c]). */
 int b200_gated_recurrence_scan(const float* u, const float* gates, const float* gate_bias, const float* lam, const void* proj,
                                int f32, int64_t ld, int y_col, const float* y_bias, const int32_t* cu_seq,
                                const int32_t* ctx_lens, const int32_t* state_slots, float* S, void* out, int64_t ldo,
                                int n_seqs, int W, float gate_c, void* stream);
+/* The same for prompt portions, in chunks of b200_gated_recurrence_chunk_rows() rows that run side by side
+ * (workspace: 2 * (T / chunk + n_seqs + 1) * W floats; max_len: the longest portion). */
+int b200_gated_recurrence_chunk_rows(void);
+int b200_gated_recurrence_scan_chunked(const float* u, const float* gates, const float* gate_bias, const float* lam,
+                                       const void* proj, int f32, int64_t ld, int y_col, const float* y_bias,
+                                       const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S,
+                                       void* out, int64_t ldo, int n_seqs, int W, float gate_c, int T, int max_len,
+                                       float* workspace, int64_t workspace_floats, void* stream);
 /* Linear attention with a decay per key channel and token, alpha = sigmoid(z)^inv_tau: S [slots][H][dv][dk]. */
 int b200_gla_scan(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* z, int64_t ldz, float inv_tau,
                   const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S, float* o_raw,

@@ -40,7 +40,7 @@ def test_config_reader_round_trip_and_rejections(tmp_path):
     assert a.kind == "attention" and a.gate and a.gate_per_head and a.gate_width == 4 and a.rot.layout == "half" and not a.window
     assert b.kv_from == 2 and c.kv_owner(3) == 2 and c.kv_owner(1) == 1 and c.kv_owner(0) is None
     assert c.layers[0].mlp.act == "clamped_swish" and c.layers[0].mlp.limit == 1.5
-    assert not a.tile_sized and not p.left.tile_sized
+    assert not a.tile_sized and not p.left.tile_sized      # 6-wide keys; pooled blocks are not on the tensor-core kernels
     assert p.left.pool_per_page(16) == 6
     back = LayerListConfig.from_dict(json.loads(json.dumps(c.to_dict())))
     assert back == c

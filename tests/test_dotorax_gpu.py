@@ -80,7 +80,17 @@ def cfg_plain():
                        dict(_par(2, 2, 16, 4, 4, 3, 1, 16, 4, 2), mlp=_ff(24))]}
 
 
-CFGS = {"odd": cfg_odd, "tiles": cfg_tiles, "plain": cfg_plain}
+def cfg_wide():
+    """128-wide heads in groups of four: in bf16 the attention layers (one of them on another layer's keys and values)
+    run on the tcgen05 prefill and split-KV decode kernels with their one gate per head."""
+    return {"architecture": "Dotorax", "vocab": 256, "width": 256, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "canon": {"taps": 3}, "max_positions": 512,
+            "layers": [dict(_attn(8, 2, 128, 128, 32, base=5e5), mlp=_ff(128)),
+                       dict(_par(4, 1, 128, 128, 64, 40, 8, 256, 4, 3), mlp=_ff(128)),
+                       dict(_attn(8, 2, 128, 128, 32, base=5e5, kv_from=0), mlp=_ff(128))]}
+
+
+CFGS = {"odd": cfg_odd, "tiles": cfg_tiles, "plain": cfg_plain, "wide": cfg_wide}
 
 
 def _engine(cfg, weights, dtype, blocks=64, seqs=4, mbt=256, eager=False, max_len=512):
@@ -360,6 +370,60 @@ def test_rotated_attention_with_one_gate_per_head_and_queries_only_for_a_borrowe
         od = torch.zeros(1, H * dv, dtype=dtype, device="cuda")
         ops.attn_sink_decode(proj[n - 1:], gate_col, kc, vc, bt, _i32([n]), None, od, H, G, dk, dv, scale, gate_per_head=True)
         assert _rel(od, want.reshape(n, -1)[n - 1:]) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("H,G,dk,n,start,splits", [(8, 2, 128, 200, 0, 1), (8, 1, 128, 150, 37, 3), (4, 2, 64, 90, 0, 2)])
+def test_one_gate_per_head_on_the_tensor_core_attention_kernels(H, G, dk, n, start, splits):
+    """bf16, tile-sized heads: the tcgen05 prefill kernel (128-wide heads in groups of four and eight) and the split-KV
+    decode kernel multiply a head's output by sigmoid of the head's ONE gate column."""
+    from gpustack_b200 import ops
+
+    scale = 0.09
+    q, k, v = _pool_case(BF, n, H, G, dk, dk, seed=31)
+    gate = _rnd(n, 8, seed=32, scale=2.0).to(BF)           # H gate columns, padded to 16-byte rows
+    want = (O.causal_attention(q.to(F64), k.to(F64), v.to(F64), scale) * torch.sigmoid(gate[:, :H].to(F64)).unsqueeze(-1)).reshape(n, -1)
+    kc, vc, perm = _paged(k, v, BF, 5)
+    bt = perm.cuda().reshape(1, -1)
+    rows = torch.cat([q.reshape(n, H * dk), gate], dim=1)[start:].cuda().contiguous()      # [q | gate columns]
+    if ops.attn_prefill_tc_covers(H, G, dk):
+        out = torch.zeros(n - start, H * dk, dtype=BF, device="cuda")
+        ts, tq = ops.build_prefill_tiles([n - start], ops.attn_prefill_tile(H, G), [start])
+        ops.paged_attn_prefill_ex(rows, rows.stride(0), kc, vc, bt, _i32([0, n - start]), _i32([start]), _i32(ts), _i32(tq), out,
+                                  H, G, dk, scale, gate=rows[:, H * dk:], gate_per_head=True)
+        assert _rel(out, want[start:]) < KTOL[BF]
+    last = rows[-1:]
+    od = torch.zeros(1, H * dk, dtype=BF, device="cuda")
+    ws = ops.attn_decode_workspace(1, H, dk, splits, "cuda")
+    ops.paged_attn_decode(last, last.stride(0), kc, vc, bt, _i32([n]), od, H, G, dk, scale, num_splits=splits, workspace=ws,
+                          gate=last[:, H * dk:], gate_per_head=True)
+    assert _rel(od, want[n - 1:]) < KTOL[BF]
+
+
+@pytest.mark.parametrize("H,G,window,pool,n,start", [(8, 2, 40, 8, 300, 0), (4, 1, 64, 5, 260, 33), (8, 1, 24, 16, 200, 128),
+                                                      (8, 2, 500, 4, 150, 0)])
+def test_window_on_the_tensor_cores_continued_over_the_pooled_blocks(H, G, window, pool, n, start):
+    """bf16, 128-wide heads: the tcgen05 kernel attends the window's tokens and hands over every row's log-sum-exp; the
+    generic kernel continues that softmax over the pooled blocks.  The per-head temperature rides in the queries."""
+    from gpustack_b200 import ops
+
+    dk, scale = 128, 0.09
+    temp = 1.0 + 0.3 * _rnd(H, seed=9)
+    q, k, v = _pool_case(BF, n, H, G, dk, dk, seed=41)
+    want = O.pooled_window_attention(q.to(F64), k.to(F64), v.to(F64), scale * temp.to(F64), window, pool).reshape(n, -1)
+    kc, vc, perm = _paged(k, v, BF, 7)
+    pk = torch.zeros(kc.shape[0], G, -(-16 // pool), dk, device="cuda")
+    pv = torch.zeros_like(pk)
+    bt = perm.cuda().reshape(1, -1)
+    ops.kv_pool_update(kc, vc, pk, pv, bt, _i32([0, n]), _i32([0]), 1, n, pool)
+    rows = (q.float() * temp.reshape(1, H, 1)).to(BF)[start:].reshape(n - start, H * dk).cuda().contiguous()
+    out = torch.zeros_like(rows)
+    lse = torch.zeros(n - start, H, device="cuda")
+    tile = ops.attn_prefill_tile(H, G)
+    ts, tq = ops.build_prefill_tiles([n - start], tile, [start])
+    args = (bt, _i32([0, n - start]), _i32([start]), _i32(ts), _i32(tq))
+    ops.paged_attn_prefill_ex(rows, rows.stride(0), kc, vc, *args, out, H, G, dk, scale, window=window, lse_out=lse)
+    ops.attn_sink_prefill_more(rows, kc, *args, out, lse, H, G, dk, dk, scale, tile, window, None, (pk, pv, pool))
+    assert _rel(out, want[start:]) < KTOL[BF]
 
 
 @pytest.mark.parametrize("W,blocks", [(21, 3), (128, 2), (10, 1), (96, 12)])
