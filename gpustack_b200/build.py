@@ -104,7 +104,9 @@ SANDWICH_SOURCES = [
 def layer_list_sources(mcfg):
     """(tag, sources) of the library a process serving this layer-list model needs."""
     if getattr(mcfg, "residual", "post_ln") == "sandwich":
-        tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)
+        attn = [l.mixer if l.mixer.kind == "attention" else l.mixer.left for l in mcfg.layers
+                if l.mixer.kind in ("attention", "side_by_side")]
+        tc = any(a.tokens_tile_sized for a in attn)       # a window's tokens too, when pooled blocks follow
         return ("sandwich_tc", SANDWICH_SOURCES + ATTENTION_TC_SOURCES) if tc else ("sandwich", list(SANDWICH_SOURCES))
     if getattr(mcfg, "residual", "post_ln") == "parallel":
         routed = any(l.mlp is not None and l.mlp.kind == "moe" for l in mcfg.layers)

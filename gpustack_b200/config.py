@@ -249,7 +249,13 @@ class AttentionSpec:
     def tile_sized(self) -> bool:
         """Keys and values share one width that is a tensor-core tile (64 / 128) and the group fits the decode
         kernel: the Llama-class attention kernels (with sink and gate) can serve this mixer in bf16."""
-        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16 and not self.pool
+        return self.tokens_tile_sized and not self.pool
+
+    @property
+    def tokens_tile_sized(self) -> bool:
+        """tile_sized without regard to pooled blocks: the tensor-core kernels can attend this mixer's TOKENS and hand
+        over every row's log-sum-exp; the pooled blocks then continue that softmax in the generic kernel."""
+        return self.dim == self.vdim and self.dim in (64, 128) and self.heads // self.kv_heads <= 16
 
     @property
     def gate_width(self) -> int:

@@ -81,7 +81,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
                          float* __restrict__ ws_o, float* __restrict__ ws_ml, int num_splits,
                          int Hq, int Hkv, float scale_log2, uint32_t* __restrict__ split_ctr,
                          const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride,
-                         int window, int gate_per_head) {
+                         int window, int gate_per_head, float* __restrict__ lse_out) {
   pdl_launch_dependents();
   pdl_wait();
   using Cfg = DecCfg<D>;
@@ -265,6 +265,9 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
     const int h = kvh * G + g;
     if (num_splits == 1) {
       out[((size_t)b * Hq + h) * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, h, D, d, gate_per_head);
+      // the row's log-sum-exp over its keys (natural logarithm; the sink is not in it), for a caller that goes on
+      if (lse_out != nullptr && d == 0)
+        lse_out[(size_t)b * Hq + h] = den > 0.f ? (mm + log2f(den)) * 0.6931471805599453f : -INFINITY;
     } else {
       const size_t slot = ((size_t)b * Hq + h) * num_splits + split;
       ws_o[slot * D + d] = num;
@@ -302,6 +305,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
       num += sc * __ldcg(ws_o + (row * num_splits + sp) * D + d);
     }
     out[row * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, kvh * G + g, D, d, gate_per_head);
+    if (lse_out != nullptr && d == 0) lse_out[row] = den > 0.f ? (mm + log2f(den)) * 0.6931471805599453f : -INFINITY;
   }
 }
 
@@ -751,6 +755,18 @@ extern "C" int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const 
                                          int D, int block_size, float scale, const float* sink,
                                          const void* gate, int64_t gate_stride, int window, int gate_per_head,
                                          void* stream) {
+  return b200_paged_attn_decode_lse(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_lens, out, workspace, num_splits,
+                                    B, Hq, Hkv, D, block_size, scale, sink, gate, gate_stride, window, gate_per_head, nullptr,
+                                    stream);
+}
+
+extern "C" int b200_paged_attn_decode_lse(const void* q, int64_t q_stride, const void* k_cache,
+                                          const void* v_cache, const int32_t* block_table,
+                                          int max_blocks, const int32_t* seq_lens, void* out,
+                                          void* workspace, int num_splits, int B, int Hq, int Hkv,
+                                          int D, int block_size, float scale, const float* sink,
+                                          const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                                          float* lse_out, void* stream) {
   B200_REQUIRE(window >= 0, "attn_decode: window %d", window);
   B200_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attn_decode: bad head counts");
   B200_REQUIRE(Hq / Hkv <= 16, "attn_decode: group size %d > 16 unsupported", Hq / Hkv);
@@ -779,7 +795,7 @@ extern "C" int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const 
     (void)launch_pdl(paged_attn_decode_kernel<128>, dim3(grid), dim3(kDecWarps * 32), DecCfg<128>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride, window, gate_per_head);
+        (const bf16*)gate, gate_stride, window, gate_per_head, lse_out);
     rc = b200_check_launch("b200_paged_attn_decode");
   } else {
     static bool once = false;
@@ -791,7 +807,7 @@ extern "C" int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const 
     (void)launch_pdl(paged_attn_decode_kernel<64>, dim3(grid), dim3(kDecWarps * 32), DecCfg<64>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
-        (const bf16*)gate, gate_stride, window, gate_per_head);
+        (const bf16*)gate, gate_stride, window, gate_per_head, lse_out);
     rc = b200_check_launch("b200_paged_attn_decode");
   }
   return rc;

@@ -210,6 +210,8 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
   const int row0 = cu_q[s], qlen = cu_q[s + 1] - row0, ctx = ctx_lens[s];
   if (q0 >= qlen) return;                             // a piece beyond the end of a short last tile
   const int nrows = min(kPfRows, qlen - q0);
+  // a continued softmax whose last row sees no pooled block yet: the first part's rows stand as they are
+  if (init_lse != nullptr && (pool_k == nullptr || window <= 0 || (ctx + q0 + nrows - window) / pool <= 0)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t* bt = block_table + (size_t)s * max_blocks;
   if (head_scale != nullptr) scale *= head_scale[h];
@@ -361,7 +363,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
                         int H, int G, int dk, int dv, int page, float scale, int64_t v_ld, int window, int gate_per_head,
                         const float* __restrict__ head_scale, const float* __restrict__ pool_k,
-                        const float* __restrict__ pool_v, int pool, int per_page) {
+                        const float* __restrict__ pool_v, int pool, int per_page, const float* __restrict__ init_lse) {
   __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
   extern __shared__ __align__(16) float sm_dyn[];      // [dk (padded to 8)] query, then [warps][dv] partial outputs
   constexpr int E = 16 / (int)sizeof(TA);               // elements per 16-byte load
@@ -380,6 +382,17 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
   if (warp == 0 && sink != nullptr) { m = sink[h]; l = 1.f; }
 #pragma unroll
   for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] = 0.f;
+  if (init_lse != nullptr && warp == 0) {
+    // the softmax is CONTINUED: another kernel has attended the window's tokens, `out` holds its normalised row and
+    // init_lse its log-sum-exp -- a running state with maximum lse, denominator 1 and the output as accumulator
+    m = init_lse[(size_t)b * H + h];
+    l = m > -CUDART_INF_F ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxDvPerLane; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv && l > 0.f) acc[c] = as_f32(out[(size_t)b * ldo + h * dv + d]);
+    }
+  }
   // a sliding window: the row at position n - 1 sees keys [n - window, n); the first block read is the one that holds
   // the window's first key
   const int first = window > 0 ? max(0, n - window) : 0;
@@ -395,7 +408,14 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
       base = ((size_t)bt[pj] * G + g) * per_page + (key - (pj * page + pool - 1) / pool);
       const float* kp = pool_k + base * dk;
       float a = 0.f;
-      for (int d = 0; d < dk; ++d) a = fmaf(qsm[d], kp[d], a);
+      if ((dk & 3) == 0) {                  // entries are 16-byte aligned: dk * 4 bytes each from an aligned base
+        for (int d = 0; d < dk; d += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kp + d);
+          a = fmaf(qsm[d], kv.x, a); a = fmaf(qsm[d + 1], kv.y, a); a = fmaf(qsm[d + 2], kv.z, a); a = fmaf(qsm[d + 3], kv.w, a);
+        }
+      } else {
+        for (int d = 0; d < dk; ++d) a = fmaf(qsm[d], kp[d], a);
+      }
       sc = a;
     }
     const float mn = fmaxf(m, warp_max(sc));
@@ -405,6 +425,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
     const int cnt = min(32, n_pool - k0);
+#pragma unroll 4
     for (int j = 0; j < cnt; ++j) {
       const float pj_ = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
@@ -416,7 +437,8 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
       }
     }
   }
-  for (int k0 = (first & ~31) + warp * 32; k0 < n; k0 += kDecWarps * 32) {
+  const int tok_end = init_lse != nullptr ? 0 : n;      // a continued softmax reads the pooled blocks only
+  for (int k0 = (first & ~31) + warp * 32; k0 < tok_end; k0 += kDecWarps * 32) {
     const int key = k0 + lane;
     const bool live = key < n && key >= first;
     size_t base = 0;
@@ -619,12 +641,12 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
                                    stream);
 }
 
-extern "C" int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
-                                          const void* v_cache, const int32_t* block_table, int max_blocks,
-                                          const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
-                                          int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
-                                          int gate_per_head, const float* head_scale, const float* pool_k,
-                                          const float* pool_v, int pool, int per_page, void* stream) {
+static int attn_sink_decode_launch(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                   const void* v_cache, const int32_t* block_table, int max_blocks,
+                                   const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                   int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
+                                   int gate_per_head, const float* head_scale, const float* pool_k,
+                                   const float* pool_v, int pool, int per_page, const float* init_lse, void* stream) {
   if (v_ld <= 0) v_ld = dv;
   B200_REQUIRE(pool_k == nullptr || (pool_v != nullptr && window > 0 && pool > 0 && per_page == (page + pool - 1) / pool),
                "attn_sink_decode: pooled blocks need a window, both caches and ceil(page / pool) entries per page");
@@ -643,16 +665,37 @@ extern "C" int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld,
     attn_sink_decode_kernel<TA, V, 16><<<grid, kDecWarps * 32, smem, s>>>(                                       \
         (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens, \
         sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head, head_scale, pool_k, pool_v,  \
-        pool, per_page);                                                                                         \
+        pool, per_page, init_lse);                                                                               \
   else                                                                                                           \
     attn_sink_decode_kernel<TA, V, 8><<<grid, kDecWarps * 32, smem, s>>>(                                        \
       (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
       sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld, window, gate_per_head, head_scale, pool_k, pool_v,    \
-      pool, per_page)
+      pool, per_page, init_lse)
   if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }
   else { if (vec) B200_DEC(bf16, true); else B200_DEC(bf16, false); }
 #undef B200_DEC
   return b200_check_launch("b200_attn_sink_decode");
+}
+
+extern "C" int b200_attn_sink_decode_pool(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                          const void* v_cache, const int32_t* block_table, int max_blocks,
+                                          const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                          int G, int dk, int dv, int page, float scale, int64_t v_ld, int window,
+                                          int gate_per_head, const float* head_scale, const float* pool_k,
+                                          const float* pool_v, int pool, int per_page, void* stream) {
+  return attn_sink_decode_launch(proj, f32, ld, gate_col, k_cache, v_cache, block_table, max_blocks, seq_lens, B, sink, out, ldo,
+                                 H, G, dk, dv, page, scale, v_ld, window, gate_per_head, head_scale, pool_k, pool_v, pool,
+                                 per_page, nullptr, stream);
+}
+
+extern "C" int b200_attn_sink_decode_more(const void* proj, int f32, int64_t ld, const int32_t* block_table, int max_blocks,
+                                          const int32_t* seq_lens, int B, void* out, int64_t ldo, int H, int G, int dk, int dv,
+                                          int page, float scale, int window, const float* head_scale, const float* pool_k,
+                                          const float* pool_v, int pool, int per_page, const float* init_lse, void* stream) {
+  B200_REQUIRE(init_lse != nullptr && pool_k != nullptr, "attn_sink_decode_more: needs the first part's log-sum-exp and pooled blocks");
+  // no token is read: the caches' pointers only pass the alignment test of the vector path
+  return attn_sink_decode_launch(proj, f32, ld, -1, pool_k, pool_k, block_table, max_blocks, seq_lens, B, nullptr, out, ldo, H, G,
+                                 dk, dv, page, scale, 0, window, 0, head_scale, pool_k, pool_v, pool, per_page, init_lse, stream);
 }
 
 extern "C" int b200_attn_sink_decode_ex(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,

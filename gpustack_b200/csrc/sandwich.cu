@@ -146,63 +146,97 @@ __device__ __forceinline__ int seq_of_row(const int32_t* __restrict__ cu_seq, in
 
 constexpr int kConvMaxTaps = 8;
 
-// grid (T, ceil(C / (256 V))); TI input element, TO output element; a thread takes V neighbouring channels
-template <typename TI, typename TO, int V>
+// grid (ceil(T / RB), ceil(C / (256 V))); TI input element, TO output element; a thread takes V neighbouring channels of RB
+// rows in turn, the taps' weights staying in registers (RB = 1 for small steps, which need the CTAs more than the reuse)
+template <typename TI, typename TO, int V, int RB>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __restrict__ in_bias,
                    const float* __restrict__ w, const float* __restrict__ bias, int add_input,
                    const float* __restrict__ ring, const int32_t* __restrict__ cu_seq,
                    const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ state_slots, int n_seqs, TO* out,
-                   int64_t ld_out, int C, int taps) {
-  const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-  const int s = seq_of_row(cu_seq, n_seqs, t);
-  if (c >= C) return;
-  const int ctx = ctx_lens[s], p = ctx + (t - cu_seq[s]);
-  const int R = taps - 1;
-  float ib[V], cur[V], acc[V];
-  if (V == 4) {
-    const float4 b = in_bias != nullptr ? sw_ld4(in_bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 x = sw_ld4(in + (size_t)t * ld_in + c);
-    const float4 o = bias != nullptr ? sw_ld4(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    ib[0] = b.x; ib[V > 1 ? 1 : 0] = b.y; ib[V > 2 ? 2 : 0] = b.z; ib[V > 3 ? 3 : 0] = b.w;
-    cur[0] = x.x + b.x; cur[V > 1 ? 1 : 0] = x.y + b.y; cur[V > 2 ? 2 : 0] = x.z + b.z; cur[V > 3 ? 3 : 0] = x.w + b.w;
-    acc[0] = o.x; acc[V > 1 ? 1 : 0] = o.y; acc[V > 2 ? 2 : 0] = o.z; acc[V > 3 ? 3 : 0] = o.w;
-  } else {
-    ib[0] = in_bias != nullptr ? in_bias[c] : 0.f;
-    cur[0] = sw_f32(in[(size_t)t * ld_in + c]) + ib[0];
-    acc[0] = bias != nullptr ? bias[c] : 0.f;
-  }
-#pragma unroll
-  for (int v = 0; v < V; ++v)
-    if (add_input) acc[v] += cur[v];
-  for (int j = 0; j < R; ++j) {
-    const int sp = p - R + j;                          // the position tap j multiplies
-    if (sp < 0) continue;
-    float val[V];
-    if (sp >= ctx) {
-      if (V == 4) {
-        const float4 x = sw_ld4(in + (size_t)(t - (p - sp)) * ld_in + c);
-        val[0] = x.x + ib[0]; val[V > 1 ? 1 : 0] = x.y + ib[V > 1 ? 1 : 0]; val[V > 2 ? 2 : 0] = x.z + ib[V > 2 ? 2 : 0];
-        val[V > 3 ? 3 : 0] = x.w + ib[V > 3 ? 3 : 0];
-      } else {
-        val[0] = sw_f32(in[(size_t)(t - (p - sp)) * ld_in + c]) + ib[0];
-      }
-    } else {
-      const float* rp = ring + ((size_t)state_slots[s] * R + (sp % R)) * C + c;
-      if (V == 4) {
-        const float4 x = sw_ld4(rp);
-        val[0] = x.x; val[V > 1 ? 1 : 0] = x.y; val[V > 2 ? 2 : 0] = x.z; val[V > 3 ? 3 : 0] = x.w;
-      } else {
-        val[0] = rp[0];
-      }
+                   int64_t ld_out, int T, int C, int taps) {
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  // the rows' sequences, looked up once per CTA: context length, position and ring slot of each row
+  __shared__ int sh_ctx[RB], sh_p[RB], sh_slot[RB];
+  if (threadIdx.x < RB) {
+    const int t = blockIdx.x * RB + threadIdx.x;
+    if (t < T) {
+      const int s = seq_of_row(cu_seq, n_seqs, t);
+      sh_ctx[threadIdx.x] = ctx_lens[s];
+      sh_p[threadIdx.x] = ctx_lens[s] + (t - cu_seq[s]);
+      sh_slot[threadIdx.x] = state_slots[s];
     }
+  }
+  __syncthreads();
+  if (c >= C) return;
+  const int R = taps - 1;
+  // wd[d]: the weight of the input d positions back (d = 0: the current token, the LAST tap)
+  float wd[kConvMaxTaps][V], ib[V], ob[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[(size_t)(c + v) * taps + j], val[v], acc[v]);
+  for (int d = 0; d < kConvMaxTaps; ++d)
+#pragma unroll
+    for (int v = 0; v < V; ++v) wd[d][v] = d <= R ? w[(size_t)(c + v) * taps + (R - d)] : 0.f;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    ib[v] = in_bias != nullptr ? in_bias[c + v] : 0.f;
+    ob[v] = bias != nullptr ? bias[c + v] : 0.f;
+  }
+  auto load_row = [&](int t, float (&x)[V]) {           // row t of the input, with its bias
+    if (V == 4) {
+      const float4 q = sw_ld4(in + (size_t)t * ld_in + c);
+      x[0] = q.x + ib[0]; x[V > 1 ? 1 : 0] = q.y + ib[V > 1 ? 1 : 0]; x[V > 2 ? 2 : 0] = q.z + ib[V > 2 ? 2 : 0];
+      x[V > 3 ? 3 : 0] = q.w + ib[V > 3 ? 3 : 0];
+    } else {
+      x[0] = sw_f32(in[(size_t)t * ld_in + c]) + ib[0];
+    }
+  };
+  // all of the CTA's rows first (independent loads in flight); earlier taps then come from registers
+  float cur[RB][V];
+#pragma unroll
+  for (int i = 0; i < RB; ++i) {
+    const int t = blockIdx.x * RB + i;
+    if (t < T) {
+      load_row(t, cur[i]);
+    } else {
+#pragma unroll
+      for (int v = 0; v < V; ++v) cur[i][v] = 0.f;
+    }
   }
 #pragma unroll
-  for (int v = 0; v < V; ++v) acc[v] = fmaf(w[(size_t)(c + v) * taps + R], cur[v], acc[v]);
-  if (V == 4) sw_st4(out + (size_t)t * ld_out + c, make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]));
-  else sw_store(out + (size_t)t * ld_out + c, acc[0]);
+  for (int i = 0; i < RB; ++i) {
+    const int t = blockIdx.x * RB + i;
+    if (t >= T) break;
+    const int ctx = sh_ctx[i], p = sh_p[i];
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = fmaf(wd[0][v], cur[i][v], add_input ? ob[v] + cur[i][v] : ob[v]);
+#pragma unroll
+    for (int d = 1; d < kConvMaxTaps; ++d) {
+      const int sp = p - d;                            // the position this tap multiplies
+      if (d > R || sp < 0) continue;
+      float val[V];
+      if (sp >= ctx) {                                 // one of this step's rows of the same sequence
+        if (i - d >= 0) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) val[v] = cur[i - d >= 0 ? i - d : 0][v];
+        } else {
+          load_row(t - d, val);
+        }
+      } else {                                         // an earlier step's: the sequence's ring
+        const float* rp = ring + ((size_t)sh_slot[i] * R + (sp % R)) * C + c;
+        if (V == 4) {
+          const float4 q = sw_ld4(rp);
+          val[0] = q.x; val[V > 1 ? 1 : 0] = q.y; val[V > 2 ? 2 : 0] = q.z; val[V > 3 ? 3 : 0] = q.w;
+        } else {
+          val[0] = rp[0];
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = fmaf(wd[d][v], val[v], acc[v]);
+    }
+    if (V == 4) sw_st4(out + (size_t)t * ld_out + c, make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]));
+    else sw_store(out + (size_t)t * ld_out + c, acc[0]);
+  }
 }
 
 // grid (n_seqs, taps - 1, ceil(C / 256))
@@ -223,7 +257,7 @@ conv_commit_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __rest
 
 // grid (n_seqs, most blocks a sequence completes in this step, G); cu_q == null: one new row per sequence whose
 // context is ctx_lens[s] - 1 tokens (ctx_lens then counts the new row, as a decode step's lengths do)
-template <typename TA>
+template <typename TA, int V>
 __global__ void __launch_bounds__(128)
 kv_pool_update_kernel(const TA* __restrict__ k_cache, const TA* __restrict__ v_cache, float* pool_k, float* pool_v,
                       const int32_t* __restrict__ block_table, int max_blocks, const int32_t* __restrict__ cu_q,
@@ -239,16 +273,29 @@ kv_pool_update_kernel(const TA* __restrict__ k_cache, const TA* __restrict__ v_c
   const int idx = b - (pj * page + pool - 1) / pool;
   const size_t dst = ((size_t)bt[pj] * G + g) * per_page + idx;
   const float inv = 1.0f / (float)pool;
-  for (int c = threadIdx.x; c < dk + dv; c += blockDim.x) {
-    const bool is_k = c < dk;
-    const int cc = is_k ? c : c - dk, w = is_k ? dk : dv;
+  // a thread takes V neighbouring columns (V = 4: one 8- or 16-byte load per token); tokens are added in order
+  const int nk = dk / V, nv = dv / V;
+  for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
+    const bool is_k = c < nk;
+    const int cc = (is_k ? c : c - nk) * V, w = is_k ? dk : dv;
     const TA* cache = is_k ? k_cache : v_cache;
-    float sum = 0.f;
+    float sum[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) sum[v] = 0.f;
+#pragma unroll 4
     for (int i = 0; i < pool; ++i) {
       const int tok = first + i;
-      sum += sw_f32(cache[(((size_t)bt[tok / page] * G + g) * page + (tok % page)) * w + cc]);
+      const TA* src = cache + (((size_t)bt[tok / page] * G + g) * page + (tok % page)) * w + cc;
+      if (V == 4) {
+        const float4 t = sw_ld4(src);
+        sum[0] += t.x; sum[V > 1 ? 1 : 0] += t.y; sum[V > 2 ? 2 : 0] += t.z; sum[V > 3 ? 3 : 0] += t.w;
+      } else {
+        sum[0] += sw_f32(src[0]);
+      }
     }
-    (is_k ? pool_k : pool_v)[dst * w + cc] = sum * inv;
+    float* out = (is_k ? pool_k : pool_v) + dst * w + cc;
+    if (V == 4) sw_st4(out, make_float4(sum[0] * inv, sum[V > 1 ? 1 : 0] * inv, sum[V > 2 ? 2 : 0] * inv, sum[V > 3 ? 3 : 0] * inv));
+    else out[0] = sum[0] * inv;
   }
 }
 
@@ -301,19 +348,20 @@ extern "C" int b200_causal_conv(const void* in, int in_f32, int64_t ld_in, const
   const bool vec = C % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && al(in, in_f32 ? 16 : 8) && al(out, out_f32 ? 16 : 8) &&
                    al(in_bias, 16) && al(bias, 16) && al(ring, 16);
   const int V = vec ? 4 : 1;
-  dim3 grid(T, (C + 256 * V - 1) / (256 * V));
+  const int rb = T >= 2048 ? 8 : 1;
+  dim3 grid((T + rb - 1) / rb, (C + 256 * V - 1) / (256 * V));
+#define B200_CC2(TI, TO, VV, RB)                                                                                      \
+  causal_conv_kernel<TI, TO, VV, RB><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, \
+                                                          ctx_lens, state_slots, n_seqs, (TO*)out, ld_out, T, C, taps)
 #define B200_CC(TI, TO)                                                                                               \
   do {                                                                                                                \
-    if (vec)                                                                                                          \
-      causal_conv_kernel<TI, TO, 4><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, \
-                                                         ctx_lens, state_slots, n_seqs, (TO*)out, ld_out, C, taps);   \
-    else                                                                                                              \
-      causal_conv_kernel<TI, TO, 1><<<grid, 256, 0, s>>>((const TI*)in, ld_in, in_bias, w, bias, add_input, ring, cu_seq, \
-                                                         ctx_lens, state_slots, n_seqs, (TO*)out, ld_out, C, taps);   \
+    if (vec) { if (rb == 8) B200_CC2(TI, TO, 4, 8); else B200_CC2(TI, TO, 4, 1); }                                    \
+    else { if (rb == 8) B200_CC2(TI, TO, 1, 8); else B200_CC2(TI, TO, 1, 1); }                                        \
   } while (0)
   if (in_f32) { if (out_f32) B200_CC(float, float); else B200_CC(float, bf16); }
   else { if (out_f32) B200_CC(bf16, float); else B200_CC(bf16, bf16); }
 #undef B200_CC
+#undef B200_CC2
   return b200_check_launch("b200_causal_conv");
 }
 
@@ -340,11 +388,14 @@ extern "C" int b200_kv_pool_update(const void* k_cache, const void* v_cache, int
   if (n_seqs == 0 || max_new <= 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(n_seqs, max_new / pool + 1, G);
-  if (f32)
-    kv_pool_update_kernel<float><<<grid, 128, 0, s>>>((const float*)k_cache, (const float*)v_cache, pool_k, pool_v, block_table,
-                                                      max_blocks, cu_q, ctx_lens, G, dk, dv, page, pool, per_page);
-  else
-    kv_pool_update_kernel<bf16><<<grid, 128, 0, s>>>((const bf16*)k_cache, (const bf16*)v_cache, pool_k, pool_v, block_table,
-                                                     max_blocks, cu_q, ctx_lens, G, dk, dv, page, pool, per_page);
+  auto al = [](const void* p, int n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+  const bool vec = dk % 4 == 0 && dv % 4 == 0 && al(k_cache, 16) && al(v_cache, 16) && al(pool_k, 16) && al(pool_v, 16);
+  const int threads = vec ? 64 : 128;
+#define B200_KP(TA, V)                                                                                             \
+  kv_pool_update_kernel<TA, V><<<grid, threads, 0, s>>>((const TA*)k_cache, (const TA*)v_cache, pool_k, pool_v, block_table, \
+                                                        max_blocks, cu_q, ctx_lens, G, dk, dv, page, pool, per_page)
+  if (f32) { if (vec) B200_KP(float, 4); else B200_KP(float, 1); }
+  else { if (vec) B200_KP(bf16, 4); else B200_KP(bf16, 1); }
+#undef B200_KP
   return b200_check_launch("b200_kv_pool_update");
 }

@@ -775,16 +775,26 @@ def _kernel_numbers_dotorax(size, T, B, ctx, log):
                                                    workspace=ws, sink=sink, gate=gB), flush)
     kvb = B * ctx * G * hd * 2 * 2.0
     put("attention decode, head gate", t_new, kvb, "attention decode, sink + gate tc", t_like_d, kvb, "bytes")
-    t_new = _time(lambda: ops.attn_sink_decode(pB, -1, kc, vc, btd, lens, None, outd, H, G, hd, hd, hd ** -0.5, window=win,
+    t_gen = _time(lambda: ops.attn_sink_decode(pB, -1, kc, vc, btd, lens, None, outd, H, G, hd, hd, hd ** -0.5, window=win,
                                                head_scale=temp, pool=(pk, pv, pool)), flush)
     sp_w = ops.attn_decode_splits(B, G, min(ctx + 16, win))
     ws_w = ops.attn_decode_workspace(B, H, hd, sp_w, dev)
     prB = projr[:B]
+    lse_d = torch.empty(B, H, device=dev)
+
+    def window_then_pooled_rows():
+        ops.paged_attn_decode(pB, Wp, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=sp_w, workspace=ws_w, window=win,
+                              lse_out=lse_d)
+        ops.attn_sink_decode_more(pB, kc, btd, lens, outd, lse_d, H, G, hd, hd, hd ** -0.5, win, None, (pk, pv, pool))
+
+    t_new = _time(window_then_pooled_rows, flush)
     t_like_w = _time(lambda: ops.paged_attn_decode(prB, projr.shape[1], kc, kc, btd, lens, outd, H, G, hd, hd ** -0.5,
                                                    num_splits=sp_w, workspace=ws_w, window=win), flush)
     kvw = B * min(ctx, win) * G * hd * 2 * 2.0
     kvp = kvw + B * max(0, (ctx - win) // pool) * G * hd * 2 * 4.0
     put("attention decode, window + pooled", t_new, kvp, "attention decode, window tc", t_like_w, kvw, "bytes")
+    put("attention decode, window + pooled (generic kernel alone)", t_gen, kvp, "attention decode, window tc", t_like_w, kvw,
+        "bytes")
 
     # ---- gated diagonal recurrence (conv + gate projections + scan) vs the decayed linear attention's closing kernel
     Wd = D
@@ -827,14 +837,14 @@ def _kernel_numbers_dotorax(size, T, B, ctx, log):
     Sg = torch.zeros(max(S, B), Hm, hd, dkg, device=dev)
     og = torch.empty(T, Hm * hd, device=dev)
     decay = torch.tensor([0.97] * Hm, dtype=f32, device=dev)
-    t_new = _time(lambda: ops.gla_scan(xg, 0, Hm * dkg, 2 * Hm * dkg, z, 1.0 / 16, cu, ctx0, slot_s, Sg, og, Hm, dkg, hd), flush,
+    t_new = _time(lambda: ops.gla_scan(xg, 0, Hm * dkg, 2 * Hm * dkg, z, 1.0 / 16, cu, ctx0, slot_s, Sg, og, Hm, dkg, hd, max_len=L), flush,
                   iters=3, warm=1)
     t_like = _time(lambda: ops.linattn_scan(xg, 0, Hm * dkg, 2 * Hm * dkg, decay, cu, ctx0, slot_s, Sg, og, Hm, dkg, hd, max_len=L),
                    flush)
     wl = 4.0 * T * Hm * dkg * hd
     put("gla_scan (prefill)", t_new, wl, "linattn_scan (prefill, chunk)", t_like, wl, "flops")
     xB, zB, oB = xg[:B], z[:B], og[:B]
-    t_new = _time(lambda: ops.gla_scan(xB, 0, Hm * dkg, 2 * Hm * dkg, zB, 1.0 / 16, cud, ctxd, slot_b, Sg, oB, Hm, dkg, hd), flush)
+    t_new = _time(lambda: ops.gla_scan(xB, 0, Hm * dkg, 2 * Hm * dkg, zB, 1.0 / 16, cud, ctxd, slot_b, Sg, oB, Hm, dkg, hd, max_len=1), flush)
     t_like = _time(lambda: ops.linattn_scan(xB, 0, Hm * dkg, 2 * Hm * dkg, decay, cud, ctxd, slot_b, Sg, oB, Hm, dkg, hd, max_len=1),
                    flush)
     put("gla_scan (decode)", t_new, B * Hm * dkg * hd * 8.0, "linattn_scan (decode)", t_like, B * Hm * dkg * hd * 8.0, "bytes")

@@ -97,6 +97,8 @@ class LayerListRunner(ModelRunner):
         # the pooled blocks by the generic kernel that continues that softmax
         self.pool_tc = {l: bool(bf and ops.LAYER_LIST_TC and m.pool and m.dim == m.vdim and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim)
                                 and ops.attn_prefill_tile(m.heads, m.kv_heads) == self.prefill_tile) for l, m in attn}
+        # ... and single rows on the split-KV decode kernel in the same way
+        self.pool_dec = {l: bool(bf and ops.LAYER_LIST_TC and m.pool and m.tokens_tile_sized) for l, m in attn}
         if self.prefill_tile % base:
             raise B200Error("prefill tile sizes of the attention kernels do not nest")
         self._dec_ws = {}
@@ -122,7 +124,9 @@ class LayerListRunner(ModelRunner):
         lin = [l.mixer for l in cfg.layers if l.mixer.kind in ("linear_attention", "gated_linear_attention")]
         gla = [l.mixer for l in cfg.layers if l.mixer.kind == "gated_linear_attention"]
         gdr = [l.mixer.right for l in cfg.layers if l.mixer.kind == "side_by_side"]
-        self.gate_width = max([2 * m.heads for m in rec] + [m.heads * m.dim for m in gla] + [2 * m.width for m in gdr] or [0])
+        # (a side-by-side mixer's attention also parks its rows' log-sum-exp here, one number per head)
+        self.gate_width = max([2 * m.heads for m in rec] + [m.heads * m.dim for m in gla] + [2 * m.width for m in gdr]
+                              + [l.mixer.left.heads for l in cfg.layers if l.mixer.kind == "side_by_side"] or [0])
         self.rec_width = max([m.out_width for m in rec + lin] or [0])
         self.lin_width = max([2 * m.heads * m.dim + m.out_width for m in lin] + [m.width for m in gdr] or [0])
         self.state: List[Optional[tuple]] = [None] * len(self.runs)
@@ -386,7 +390,8 @@ class LayerListRunner(ModelRunner):
                 z = self._view(self.gates, T, kc)
                 ops.linear(proj[:, ac:ac + m.decay_rank], lw.decay_up, z, bias=lw.decay_bias)
                 o_raw = self._view(self.o_raw, T, H * dv)
-                ops.gla_scan(x32, 0, kc, vc, z, 1.0 / m.tau, cu_all, ctx_all, slots_all, self.state[l][0], o_raw, H, dk, dv)
+                ops.gla_scan(x32, 0, kc, vc, z, 1.0 / m.tau, cu_all, ctx_all, slots_all, self.state[l][0], o_raw, H, dk, dv,
+                             max_len=Tp if Tp else 1)
                 ops.linattn_out(o_raw, proj, gc, lw.out_norm, out, H, dv, eps, False, "silu")
                 self.stats["kernel_launches"] += 5
             elif m.kind == "latent_attention":
@@ -484,12 +489,14 @@ class LayerListRunner(ModelRunner):
         right = self.mix_out[T * a.out_width:T * (a.out_width + W)].view(T, W)
         kc, vc = self.k_cache[l], self.v_cache[l]
         li = self.runs[l][0]
-        tc = nt and self.pool_tc.get(li, False)
-        # the per-head temperature rides in the query (tensor-core route: its kernel has one scale) or in the kernel
+        tc, dec = nt and self.pool_tc.get(li, False), Bd and self.pool_dec.get(li, False)
+        # the per-head temperature rides in the query (a layer with a tensor-core route: those kernels have one scale) or
+        # in the kernel; which one is the layer's property, not the step's, so a row's logits do not depend on the batch
+        qmul = self.pool_tc.get(li, False) or self.pool_dec.get(li, False)
         ops.rot_prep(proj, 0, H * dk, (H + G) * dk, self._pos, self._slots, proj, kc, vc, H, G, dk, dv, paged=True,
                      rot_dims=a.rot.dims, half_layout=a.rot.layout == "half", freq=lw.rot_freq, unit_norm=a.qk_unit_norm, eps=eps,
-                     q_head_mul=lw.head_scale if (tc and lw.head_scale is not None) else None)
-        hs = None if tc else lw.head_scale
+                     q_head_mul=lw.head_scale if (qmul and lw.head_scale is not None) else None)
+        hs = None if qmul else lw.head_scale
         pool = None
         if a.pool:
             pool = (self.pool_k[l], self.pool_v[l], a.pool)
@@ -507,7 +514,14 @@ class LayerListRunner(ModelRunner):
         elif nt:
             ops.attn_sink_prefill(proj[:Tp], -1, kc, vc, bt_p, cu_p, ctx_p, ts, tq, None, left[:Tp], H, G, dk, dv, a.scale,
                                   tile_rows=self.prefill_tile, window=a.window, head_scale=hs, pool=pool)
-        if Bd:
+        if dec:
+            splits, ws = self._decode_plan(Bd, a)
+            lse = self._view(self.gates, T, H)[Tp:T]
+            ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, left[Tp:T], H, G, dk, a.scale,
+                                  num_splits=splits, workspace=ws, window=a.window, lse_out=lse)
+            ops.attn_sink_decode_more(proj[Tp:T], kc, bt_d, lens_d, left[Tp:T], lse, H, G, dk, dv, a.scale, a.window, None, pool)
+            self.stats["kernel_launches"] += 1
+        elif Bd:
             ops.attn_sink_decode(proj[Tp:T], -1, kc, vc, bt_d, lens_d, None, left[Tp:T], H, G, dk, dv, a.scale,
                                  window=a.window, head_scale=hs, pool=pool)
         y_col = a.q_width + G * (dk + dv)

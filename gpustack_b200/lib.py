@@ -153,6 +153,10 @@ SIGNATURES = {
                                 _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _f32, _vp, _vp]),
     "b200_paged_attn_decode_hg": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
                                          _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b200_paged_attn_decode_lse": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
+                                          _i32, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp, _vp]),
+    "b200_attn_sink_decode_more": (_i32, [_vp, _i32, _i64, _vp, _i32, _vp, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _i32,
+                                          _f32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "b200_gated_recurrence_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32,
                                           _i32, _f32, _vp]),
     "b200_gated_recurrence_chunk_rows": (_i32, []),
@@ -160,6 +164,8 @@ SIGNATURES = {
                                                   _i32, _i32, _f32, _i32, _i32, _vp, _i64, _vp]),
     "b200_gla_scan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
                              _vp]),
+    "b200_gla_scan_rows": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
+                             _i32, _vp]),
 }
 
 # A process that serves ONE model family may ask for a library linked from that family's sources only

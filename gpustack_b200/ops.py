@@ -367,17 +367,20 @@ def attn_decode_workspace(B, Hq, D, num_splits, device) -> torch.Tensor:
 
 
 def paged_attn_decode(q, q_stride, k_cache, v_cache, block_table, seq_lens, out, Hq, Hkv, D, scale,
-                      num_splits=1, workspace=None, sink=None, gate=None, window: int = 0, gate_per_head: bool = False):
+                      num_splits=1, workspace=None, sink=None, gate=None, window: int = 0, gate_per_head: bool = False,
+                      lse_out=None):
     """q: [B, >=Hq*D] view into the qkv buffer (row stride q_stride elements).  sink [Hq] fp32: softmax sink;
     gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate) -- with gate_per_head
     the view holds ONE number per head, [B, >=Hq]; window > 0: the row at position n - 1 sees keys [n - window, n)."""
     B = seq_lens.shape[0]
     _req(block_table, torch.int32, "block_table"); _req(seq_lens, torch.int32, "seq_lens")
-    check(load().b200_paged_attn_decode_hg(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
-                                           block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
-                                           num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
-                                           0 if gate is None else gate.stride(0), int(window), 1 if gate_per_head else 0,
-                                           _stream()), "paged_attn_decode")
+    if lse_out is not None:       # fp32 [B, Hq]: every row's log-sum-exp, for attn_sink_decode_more
+        _req(lse_out, torch.float32, "lse_out")
+    check(load().b200_paged_attn_decode_lse(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
+                                            block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
+                                            num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
+                                            0 if gate is None else gate.stride(0), int(window), 1 if gate_per_head else 0,
+                                            _p(lse_out), _stream()), "paged_attn_decode")
     return out
 
 
@@ -580,6 +583,20 @@ def attn_sink_prefill_more(proj, k_cache, block_table, cu_q, ctx_lens, tile_seq,
     return out
 
 
+def attn_sink_decode_more(proj, k_cache, block_table, seq_lens, out, init_lse, H, G, dk, dv, scale, window: int, head_scale,
+                          pool):
+    """Single rows: continues a softmax over the pooled blocks.  `out` holds the normalised attention over the window's
+    tokens (another kernel's), init_lse [B, H] its log-sum-exp; `out` is rewritten with the joint result."""
+    _cuda(proj, block_table, seq_lens, out, init_lse, head_scale)
+    _req(init_lse, torch.float32, "init_lse")
+    pk, pv, pn, ppp = _pool_args(pool, k_cache, dk, dv)
+    check(load().b200_attn_sink_decode_more(_p(proj), _is_f32(proj), proj.stride(0), _p(block_table), block_table.shape[1],
+                                            _p(seq_lens), seq_lens.shape[0], _p(out), out.stride(0), H, G, dk, dv,
+                                            k_cache.shape[2], scale, int(window), _p(head_scale), pk, pv, pn, ppp, _p(init_lse),
+                                            _stream()), "attn_sink_decode_more")
+    return out
+
+
 def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale,
                      v_ld: int = 0, window: int = 0, gate_per_head: bool = False, head_scale=None, pool=None):
     _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out, head_scale)
@@ -760,12 +777,14 @@ def gated_recurrence_scan(u, gates, gate_bias, lam, proj, y_col: int, y_bias, cu
     return out
 
 
-def gla_scan(x, q_col: int, k_col: int, v_col: int, z, inv_tau: float, cu_seq, ctx_lens, state_slots, S, o_raw, H, dk, dv):
+def gla_scan(x, q_col: int, k_col: int, v_col: int, z, inv_tau: float, cu_seq, ctx_lens, state_slots, S, o_raw, H, dk, dv,
+             max_len: int = 0):
     """Linear attention with the decay sigmoid(z)^inv_tau per key channel and token (csrc/gated_linear_attn.cu)."""
     _cuda(x, z, cu_seq, ctx_lens, state_slots, S, o_raw)
     _req(x, torch.float32, "x"); _req(z, torch.float32, "z"); _req(S, torch.float32, "S"); _req(o_raw, torch.float32, "o_raw")
-    check(load().b200_gla_scan(_p(x), x.stride(0), q_col, k_col, v_col, _p(z), z.stride(0), inv_tau, _p(cu_seq), _p(ctx_lens),
-                               _p(state_slots), _p(S), _p(o_raw), state_slots.shape[0], H, dk, dv, _stream()), "gla_scan")
+    check(load().b200_gla_scan_rows(_p(x), x.stride(0), q_col, k_col, v_col, _p(z), z.stride(0), inv_tau, _p(cu_seq), _p(ctx_lens),
+                                    _p(state_slots), _p(S), _p(o_raw), state_slots.shape[0], H, dk, dv, int(max_len), _stream()),
+          "gla_scan")
 
 
 # ------------------------------------------- residual streams, latent attention, gated / routed feed-forward

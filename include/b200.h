@@ -487,6 +487,19 @@ int b200_paged_attn_decode_hg(const void* q, int64_t q_stride, const void* k_cac
                               void* workspace, int num_splits, int B, int Hq, int Hkv, int D, int block_size, float scale,
                               const float* sink, const void* gate, int64_t gate_stride, int window, int gate_per_head,
                               void* stream);
+/* ... and lse_out [B][Hq] (fp32, may be NULL): every row's log-sum-exp over the keys it attended, for a caller that
+ * continues the softmax over more keys (b200_attn_sink_decode_more). */
+int b200_paged_attn_decode_lse(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                               const int32_t* block_table, int max_blocks, const int32_t* seq_lens, void* out,
+                               void* workspace, int num_splits, int B, int Hq, int Hkv, int D, int block_size, float scale,
+                               const float* sink, const void* gate, int64_t gate_stride, int window, int gate_per_head,
+                               float* lse_out, void* stream);
+/* b200_attn_sink_decode_pool that CONTINUES a softmax over the pooled blocks alone: `out` holds the normalised attention
+ * over the window's tokens (another kernel's) and init_lse [B][H] its log-sum-exp; `out` is rewritten. */
+int b200_attn_sink_decode_more(const void* proj, int f32, int64_t ld, const int32_t* block_table, int max_blocks,
+                               const int32_t* seq_lens, int B, void* out, int64_t ldo, int H, int G, int dk, int dv, int page,
+                               float scale, int window, const float* head_scale, const float* pool_k, const float* pool_v,
+                               int pool, int per_page, const float* init_lse, void* stream);
 /* b200_attn_sink_prefill_pool that CONTINUES a softmax: the window's tokens have been attended by another kernel, which
  * left its normalised output in `out` and every row's log-sum-exp in init_lse [T][H]; only the pooled blocks are read
  * here and `out` is rewritten with the joint result. */
@@ -519,6 +532,11 @@ int b200_gated_recurrence_scan_chunked(const float* u, const float* gates, const
 int b200_gla_scan(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* z, int64_t ldz, float inv_tau,
                   const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S, float* o_raw,
                   int n_seqs, int H, int dk, int dv, void* stream);
+/* ... with max_len, an upper bound of the new rows per sequence (0: unknown): single rows take the kernel that reads and
+ * writes the state in whole lines. */
+int b200_gla_scan_rows(const float* x, int64_t ld, int q_col, int k_col, int v_col, const float* z, int64_t ldz, float inv_tau,
+                  const int32_t* cu_seq, const int32_t* ctx_lens, const int32_t* state_slots, float* S, float* o_raw,
+                  int n_seqs, int H, int dk, int dv, int max_len, void* stream);
 
 #ifdef __cplusplus
 }

@@ -124,6 +124,14 @@ def test_library_subset_of_a_sandwich_residual_model():
               "b200_gemm_bf16_gated", "b200_sample_f32", "b200_last_error"):
         assert hasattr(h, n), n
     assert not hasattr(h, "b200_mlstm_scan") and not hasattr(h, "b200_latent_prep")
+    # tile-sized heads in the windowed attention alone (pooled blocks follow): the tensor-core attention sources join,
+    # since the window's tokens run on them
+    d = _cfg()
+    d["layers"][1]["mixer"]["left"].update(dim=64, vdim=64, rot={"base": 50.0, "dims": 16})
+    w = LayerListConfig.from_dict(d)
+    assert w.layers[1].mixer.left.tokens_tile_sized and not w.layers[1].mixer.left.tile_sized
+    tag, srcs = build.layer_list_sources(w)
+    assert tag == "sandwich_tc" and {"attention.cu", "attention_prefill_tc.cu"} <= set(srcs)
 
 
 def test_vram_estimate_counts_pooled_blocks_rings_and_states():

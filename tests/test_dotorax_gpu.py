@@ -399,14 +399,16 @@ def test_one_gate_per_head_on_the_tensor_core_attention_kernels(H, G, dk, n, sta
     assert _rel(od, want[n - 1:]) < KTOL[BF]
 
 
-@pytest.mark.parametrize("H,G,window,pool,n,start", [(8, 2, 40, 8, 300, 0), (4, 1, 64, 5, 260, 33), (8, 1, 24, 16, 200, 128),
-                                                      (8, 2, 500, 4, 150, 0)])
-def test_window_on_the_tensor_cores_continued_over_the_pooled_blocks(H, G, window, pool, n, start):
-    """bf16, 128-wide heads: the tcgen05 kernel attends the window's tokens and hands over every row's log-sum-exp; the
-    generic kernel continues that softmax over the pooled blocks.  The per-head temperature rides in the queries."""
+@pytest.mark.parametrize("H,G,dk,window,pool,n,start", [(8, 2, 128, 40, 8, 300, 0), (4, 1, 128, 64, 5, 260, 33),
+                                                         (8, 1, 128, 24, 16, 200, 128), (8, 2, 128, 500, 4, 150, 0),
+                                                         (3, 1, 128, 33, 7, 231, 0), (12, 2, 64, 16, 3, 177, 0)])
+def test_window_on_the_tensor_cores_continued_over_the_pooled_blocks(H, G, dk, window, pool, n, start):
+    """bf16, tile-sized heads: the tcgen05 prefill kernel (128-wide heads in groups of four and eight) and the split-KV
+    decode kernel attend the window's tokens and hand over every row's log-sum-exp; the generic kernels continue that
+    softmax over the pooled blocks.  The per-head temperature rides in the queries."""
     from gpustack_b200 import ops
 
-    dk, scale = 128, 0.09
+    scale = 0.09
     temp = 1.0 + 0.3 * _rnd(H, seed=9)
     q, k, v = _pool_case(BF, n, H, G, dk, dk, seed=41)
     want = O.pooled_window_attention(q.to(F64), k.to(F64), v.to(F64), scale * temp.to(F64), window, pool).reshape(n, -1)
@@ -418,12 +420,26 @@ def test_window_on_the_tensor_cores_continued_over_the_pooled_blocks(H, G, windo
     rows = (q.float() * temp.reshape(1, H, 1)).to(BF)[start:].reshape(n - start, H * dk).cuda().contiguous()
     out = torch.zeros_like(rows)
     lse = torch.zeros(n - start, H, device="cuda")
-    tile = ops.attn_prefill_tile(H, G)
-    ts, tq = ops.build_prefill_tiles([n - start], tile, [start])
-    args = (bt, _i32([0, n - start]), _i32([start]), _i32(ts), _i32(tq))
-    ops.paged_attn_prefill_ex(rows, rows.stride(0), kc, vc, *args, out, H, G, dk, scale, window=window, lse_out=lse)
-    ops.attn_sink_prefill_more(rows, kc, *args, out, lse, H, G, dk, dk, scale, tile, window, None, (pk, pv, pool))
-    assert _rel(out, want[start:]) < KTOL[BF]
+    if ops.attn_prefill_tc_covers(H, G, dk):
+        tile = ops.attn_prefill_tile(H, G)
+        ts, tq = ops.build_prefill_tiles([n - start], tile, [start])
+        args = (bt, _i32([0, n - start]), _i32([start]), _i32(ts), _i32(tq))
+        ops.paged_attn_prefill_ex(rows, rows.stride(0), kc, vc, *args, out, H, G, dk, scale, window=window, lse_out=lse)
+        ops.attn_sink_prefill_more(rows, kc, *args, out, lse, H, G, dk, dk, scale, tile, window, None, (pk, pv, pool))
+        assert _rel(out, want[start:]) < KTOL[BF]
+    # single rows at several lengths (a pooled block that has just come into sight and one that has not yet), whole
+    # key range and split
+    for m in sorted({n, n - 1, window + pool - 1, window + pool, window + 2 * pool, max(1, window - 1)}):
+        if not start < m <= n:
+            continue
+        last = rows[m - 1 - start:m - start]
+        for splits in (1, 3):
+            od, lse1 = torch.zeros(1, H * dk, dtype=BF, device="cuda"), torch.zeros(1, H, device="cuda")
+            ws = ops.attn_decode_workspace(1, H, dk, splits, "cuda")
+            ops.paged_attn_decode(last, last.stride(0), kc, vc, bt, _i32([m]), od, H, G, dk, scale, num_splits=splits,
+                                  workspace=ws, window=window, lse_out=lse1)
+            ops.attn_sink_decode_more(last, kc, bt, _i32([m]), od, lse1, H, G, dk, dk, scale, window, None, (pk, pv, pool))
+            assert _rel(od, want[m - 1:m]) < KTOL[BF], (m, splits)
 
 
 @pytest.mark.parametrize("W,blocks", [(21, 3), (128, 2), (10, 1), (96, 12)])
@@ -469,7 +485,8 @@ def _gla_ref(q, k, v, z, tau):
     return o, S
 
 
-@pytest.mark.parametrize("H,dk,dv,tau", [(3, 10, 14, 3.0), (2, 64, 128, 8.0), (1, 8, 8, 1.0), (2, 33, 70, 16.0), (1, 128, 40, 2.0)])
+@pytest.mark.parametrize("H,dk,dv,tau", [(3, 10, 14, 3.0), (2, 64, 128, 8.0), (1, 8, 8, 1.0), (2, 33, 70, 16.0), (1, 128, 40, 2.0),
+                                          (1, 200, 24, 4.0), (2, 256, 36, 5.0)])
 def test_gated_linear_attention_in_portions_against_the_recurrence(H, dk, dv, tau):
     from gpustack_b200 import ops
 
@@ -479,13 +496,14 @@ def test_gated_linear_attention_in_portions_against_the_recurrence(H, dk, dv, ta
     q, k = x[:, :H * dk].reshape(T, H, dk), x[:, H * dk:2 * H * dk].reshape(T, H, dk)
     v = x[:, 2 * H * dk:].reshape(T, H, dv)
     want, S_end = _gla_ref(q.to(F64), k.to(F64), v.to(F64), z.to(F64), tau)
-    for cuts in ([T], [1] * T, _cuts(T, [2, 3, 16, 1, 17, 1, 5, 31])):
+    # (the bound of the new rows per sequence picks the kernel: single rows have their own; 0 = unknown)
+    for cuts, bound in (([T], T), ([1] * T, 1), ([1] * T, 0), (_cuts(T, [2, 3, 16, 1, 17, 1, 5, 31]), 31)):
         S = torch.full((3, H, dv, dk), 4.0, device="cuda")
         at, got = 0, []
         for c in cuts:
             o = torch.zeros(c, H * dv, device="cuda")
             ops.gla_scan(x[at:at + c].cuda().contiguous(), 0, H * dk, 2 * H * dk, z[at:at + c].cuda().contiguous(), 1.0 / tau,
-                         _i32([0, c]), _i32([at]), _i32([2]), S, o, H, dk, dv)
+                         _i32([0, c]), _i32([at]), _i32([2]), S, o, H, dk, dv, max_len=bound)
             got.append(o.cpu())
             at += c
         assert _rel(torch.cat(got), want.reshape(T, -1)) < 2e-5
