@@ -259,6 +259,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
     const int k0 = pooled ? it + pool_span : tok_begin + it;
     __syncthreads();                                  // previous block's K / V fully consumed (and Qs written)
     // each warp stages 8 keys
+#pragma unroll 2
     for (int jj = 0; jj < kPfKeys / kPfWarps; ++jj) {
       const int j = warp * (kPfKeys / kPfWarps) + jj;
       const int key = k0 + j;
@@ -267,13 +268,17 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
         const size_t base = ((size_t)bt[pj] * G + g) * per_page + (key - (pj * page + pool - 1) / pool);
         const float* kp = pool_k + base * dk;
         const float* vp = pool_v + base * dv;
+#pragma unroll 4
         for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = kp[d];
+#pragma unroll 4
         for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = vp[d];
       } else if (!pooled && key < kv_end) {
         const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
         const TA* kp = k_cache + base * dk;
         const TA* vp = v_cache + base * v_ld;
+#pragma unroll 4
         for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = as_f32(kp[d]);
+#pragma unroll 4
         for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = as_f32(vp[d]);
       } else {
         for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = 0.f;
@@ -409,6 +414,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
       const float* kp = pool_k + base * dk;
       float a = 0.f;
       if ((dk & 3) == 0) {                  // entries are 16-byte aligned: dk * 4 bytes each from an aligned base
+#pragma unroll 8                            // (several loads in flight: a lane walks its own row)
         for (int d = 0; d < dk; d += 4) {
           const float4 kv = *reinterpret_cast<const float4*>(kp + d);
           a = fmaf(qsm[d], kv.x, a); a = fmaf(qsm[d + 1], kv.y, a); a = fmaf(qsm[d + 2], kv.z, a); a = fmaf(qsm[d + 3], kv.w, a);
@@ -425,7 +431,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
     const int cnt = min(32, n_pool - k0);
-#pragma unroll 4
+#pragma unroll 8
     for (int j = 0; j < cnt; ++j) {
       const float pj_ = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
@@ -448,6 +454,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
       const TA* kp = k_cache + base * dk;
       float a = 0.f;
       if (VEC) {
+#pragma unroll 8
         for (int d = 0; d < dk; d += E) {
           const uint4 raw = *reinterpret_cast<const uint4*>(kp + d);
           const TA* kv = reinterpret_cast<const TA*>(&raw);
@@ -466,6 +473,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
     const int cnt = min(32, n - k0);
+#pragma unroll 8
     for (int j = max(0, first - k0); j < cnt; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);

@@ -62,25 +62,46 @@ gla_scan_kernel(const float* __restrict__ x, int64_t ld, int q_col, int k_col, i
   float S[RPW];
 #pragma unroll
   for (int j = 0; j < RPW; ++j) S[j] = (!fresh && r0 + j < dk && col < dv) ? Sp[(size_t)col * dk + r0 + j] : 0.f;
+  // a chunk's rows travel global memory -> registers -> shared memory; the NEXT chunk's loads are issued before this
+  // chunk's tokens are walked, so their latency hides behind the walk
+  constexpr int PF = (kGlTok * DKP + kGlWarps * 32 - 1) / (kGlWarps * 32), PV = kGlTok * kGlCols / (kGlWarps * 32);
+  float pq[PF], pk[PF], pz[PF], pv[PV];
+  auto fetch = [&](int ch) {
+    const int nt = min(kGlTok, t1 - ch);
+#pragma unroll
+    for (int e = 0; e < PF; ++e) {
+      const int i = threadIdx.x + e * kGlWarps * 32, tt = i / DKP, dd = i - tt * DKP;
+      pq[e] = pk[e] = pz[e] = 0.f;
+      if (i < nt * DKP && dd < dk) {
+        const float* row = x + (size_t)(ch + tt) * ld;
+        pq[e] = row[q_col + h * dk + dd];
+        pk[e] = row[k_col + h * dk + dd];
+        pz[e] = z[(size_t)(ch + tt) * ldz + h * dk + dd];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < PV; ++e) {
+      const int i = threadIdx.x + e * kGlWarps * 32, tt = i / kGlCols, cc = zc * kGlCols + (i % kGlCols);
+      pv[e] = (i < nt * kGlCols && cc < dv) ? x[(size_t)(ch + tt) * ld + v_col + h * dv + cc] : 0.f;
+    }
+  };
+  fetch(t0);
   for (int ch = t0; ch < t1; ch += kGlTok) {
     const int nt = min(kGlTok, t1 - ch);
     __syncthreads();                                  // every warp is done with the previous chunk
-    for (int i = threadIdx.x; i < nt * DKP; i += blockDim.x) {
-      const int tt = i / DKP, dd = i - tt * DKP;
-      float qv = 0.f, kv = 0.f, av = 0.f;             // rows beyond dk: their state stays zero
-      if (dd < dk) {
-        const float* row = x + (size_t)(ch + tt) * ld;
-        qv = row[q_col + h * dk + dd];
-        kv = row[k_col + h * dk + dd];
-        av = gl_alpha(z[(size_t)(ch + tt) * ldz + h * dk + dd], inv_tau);
+#pragma unroll
+    for (int e = 0; e < PF; ++e) {
+      const int i = threadIdx.x + e * kGlWarps * 32;
+      if (i < kGlTok * DKP) {
+        const int dd = i % DKP;
+        qs[i] = pq[e]; ks[i] = pk[e];
+        as[i] = dd < dk ? gl_alpha(pz[e], inv_tau) : 0.f;   // rows beyond dk: their state stays zero
       }
-      qs[i] = qv; ks[i] = kv; as[i] = av;
     }
-    for (int i = threadIdx.x; i < nt * kGlCols; i += blockDim.x) {
-      const int tt = i / kGlCols, c = zc * kGlCols + (i % kGlCols);
-      vs[i] = c < dv ? x[(size_t)(ch + tt) * ld + v_col + h * dv + c] : 0.f;
-    }
+#pragma unroll
+    for (int e = 0; e < PV; ++e) vs[threadIdx.x + e * kGlWarps * 32] = pv[e];
     __syncthreads();
+    if (ch + kGlTok < t1) fetch(ch + kGlTok);
     for (int tt = 0; tt < nt; ++tt) {
       const float v = vs[tt * kGlCols + lane];
       float kk[RPW], qq[RPW], aa[RPW];

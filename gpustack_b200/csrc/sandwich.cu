@@ -157,11 +157,12 @@ causal_conv_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __rest
                    int64_t ld_out, int T, int C, int taps) {
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
   // the rows' sequences, looked up once per CTA: context length, position and ring slot of each row
-  __shared__ int sh_ctx[RB], sh_p[RB], sh_slot[RB];
+  __shared__ int sh_ctx[RB], sh_p[RB], sh_slot[RB], sh_seq[RB];
   if (threadIdx.x < RB) {
     const int t = blockIdx.x * RB + threadIdx.x;
     if (t < T) {
       const int s = seq_of_row(cu_seq, n_seqs, t);
+      sh_seq[threadIdx.x] = s;
       sh_ctx[threadIdx.x] = ctx_lens[s];
       sh_p[threadIdx.x] = ctx_lens[s] + (t - cu_seq[s]);
       sh_slot[threadIdx.x] = state_slots[s];
@@ -201,6 +202,35 @@ causal_conv_kernel(const TI* __restrict__ in, int64_t ld_in, const float* __rest
 #pragma unroll
       for (int v = 0; v < V; ++v) cur[i][v] = 0.f;
     }
+  }
+  // the common case of a prompt step: all rows of one sequence and every tap among this step's rows -- no ring, no
+  // per-tap position arithmetic
+  const int n_rows = min(RB, T - (int)blockIdx.x * RB);
+  if (RB > 1 && sh_seq[0] == sh_seq[n_rows - 1] && sh_p[0] - R >= sh_ctx[0]) {
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      const int t = blockIdx.x * RB + i;
+      if (i >= n_rows) break;
+      float acc[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = fmaf(wd[0][v], cur[i][v], add_input ? ob[v] + cur[i][v] : ob[v]);
+#pragma unroll
+      for (int d = 1; d < kConvMaxTaps; ++d) {
+        if (d > R) break;
+        float val[V];
+        if (i - d >= 0) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) val[v] = cur[i - d >= 0 ? i - d : 0][v];
+        } else {
+          load_row(t - d, val);                        // a row of the CTA before
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(wd[d][v], val[v], acc[v]);
+      }
+      if (V == 4) sw_st4(out + (size_t)t * ld_out + c, make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]));
+      else sw_store(out + (size_t)t * ld_out + c, acc[0]);
+    }
+    return;
   }
 #pragma unroll
   for (int i = 0; i < RB; ++i) {
